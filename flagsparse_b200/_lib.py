@@ -1,0 +1,78 @@
+"""ctypes binding of libfsb.so (declared in include/fsb.h).
+
+The library is the only compute backend of this package: there is no Triton path and no CPU fallback.
+`lib()` raises if the shared library has not been built (python -m flagsparse_b200.build), so a missing
+extension is loud, never silent.
+"""
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libfsb.so")
+
+FSB_F32, FSB_F64 = 0, 1
+FSB_I32, FSB_I64 = 0, 1
+FSB_SPMV_AUTO, FSB_SPMV_VECTOR, FSB_SPMV_STREAM = 0, 1, 2
+FSB_SPMM_AUTO, FSB_SPMM_PLAIN, FSB_SPMM_BULK = 0, 1, 2
+FSB_CUDA_ERROR_BASE = 1000
+
+_ERRORS = {
+    -1: "FSB_EINVAL (bad enum, negative size or missing pointer)",
+    -2: "FSB_ERANGE (dimension outside the supported range)",
+    -3: "FSB_EALIGN (pointer not aligned to its element size)",
+    -4: "FSB_ESCRATCH (scratch buffer too small)",
+}
+
+_c = ctypes
+_vp, _i64, _i32, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_size_t
+
+# name -> (restype, argtypes); must list every symbol include/fsb.h declares
+SIGNATURES = {
+    "fsb_version": (_i32, []),
+    "fsb_spmv_tile_nnz": (_i32, [_i32, _i32]),
+    "fsb_spmm_tile_nnz": (_i32, [_i32]),
+    "fsb_csr_analyze": (_i32, [_i32, _i32, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "fsb_csr_num_tiles": (_i64, [_i64, _i32]),
+    "fsb_csr_tile_plan": (_i32, [_i32, _vp, _i64, _i64, _i32, _vp, _vp]),
+    "fsb_spmv_csr_scratch_bytes": (_sz, [_i32, _i64, _i32]),
+    "fsb_spmv_csr": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp]),
+    "fsb_spmv_csr_scatter": (
+        _i32,
+        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp],
+    ),
+    "fsb_spmm_csr_scratch_bytes": (_sz, [_i32, _i64, _i64]),
+    "fsb_spmm_csr": (
+        _i32,
+        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp, _vp],
+    ),
+}
+
+_lib = None
+
+
+def lib():
+    """Load libfsb.so once and attach the prototypes.  Raises RuntimeError when it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m flagsparse_b200.build` "
+                "(this package has no fallback path)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = handle
+    return _lib
+
+
+def check(rc, what):
+    """Turn a non-zero return code of the C ABI into a RuntimeError."""
+    if rc == 0:
+        return
+    if rc >= FSB_CUDA_ERROR_BASE:
+        raise RuntimeError(f"{what}: CUDA error {rc - FSB_CUDA_ERROR_BASE}")
+    raise RuntimeError(f"{what}: {_ERRORS.get(rc, rc)}")

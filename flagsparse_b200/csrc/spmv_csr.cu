@@ -1,0 +1,443 @@
+// CSR SpMV for sm_100a: a lanes-per-row "vector" kernel and an nnz-tiled "stream" kernel.
+//
+// Stream kernel (the load-balanced one).  The nnz range is cut into tiles of T = 256*IPT entries, so
+// every tile starts on a 16-byte boundary of `data` and `indices` whatever the row structure is and is
+// read with fully coalesced 128-bit streaming loads.  A CTA owns one tile:
+//   A  load IPT values + IPT column indices per thread, gather x through the read-only path, multiply,
+//      park the products in shared memory;
+//   B  load indptr[ra .. rb] (ra, rb from the tile plan) as tile-relative offsets into shared memory;
+//   C  segmented reduction: groups of L lanes (L = power of two picked per tile from its mean row
+//      length) each sum one row's slice of the products and finish with a shuffle tree; rows that are
+//      much longer than the tile's mean are deferred to a second pass that gives them a full warp and
+//      a double-precision accumulator.
+// Rows that end in the tile are written to y.  The one row that may continue into the next tile leaves
+// its partial sum in carry[t]; the one row that may have started before the tile leaves its partial sum
+// in head[t] instead of y.  A second tiny kernel (one thread per tile) adds head[t] and the carries of
+// the tiles the row crossed, in a fixed order, and writes y -- no floating-point atomics anywhere, so
+// the result is bit-reproducible.
+#include "fsb_common.cuh"
+
+namespace fsb {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------------------------------
+// output policies: plain local y, or the same value stored to every peer's y (row-sharded driver)
+// ---------------------------------------------------------------------------------------------------
+template <typename V>
+struct LocalOut {
+  V* y;
+  __device__ __forceinline__ void store(int64_t i, V v) const { y[i] = v; }
+};
+template <typename V>
+struct PeerOut {
+  V* const* peers;
+  int n_peers;
+  int64_t row_offset;
+  __device__ __forceinline__ void store(int64_t i, V v) const {
+    for (int p = 0; p < n_peers; ++p) peers[p][row_offset + i] = v;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------------
+// vector kernel: L lanes per row, scalar coalesced loads, two accumulators per lane
+// ---------------------------------------------------------------------------------------------------
+template <typename V, typename I, typename P, int L>
+__global__ void __launch_bounds__(kThreads) spmv_vector_kernel(const V* __restrict__ data,
+                                                              const I* __restrict__ idx,
+                                                              const P* __restrict__ ptr,
+                                                              const V* __restrict__ x, V* __restrict__ y,
+                                                              int64_t n_rows) {
+  const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  const int64_t row = gtid / L;
+  const int lane = (int)(gtid % L);
+  int64_t s = 0, e = 0;
+  if (row < n_rows) {
+    s = (int64_t)ptr[row];
+    e = (int64_t)ptr[row + 1];
+  }
+  V acc0 = 0, acc1 = 0;
+  int64_t p = s + lane;
+  for (; p + L < e; p += 2 * L) {
+    const V a0 = ld_stream(data + p), a1 = ld_stream(data + p + L);
+    const int64_t c0 = (int64_t)ld_stream(idx + p), c1 = (int64_t)ld_stream(idx + p + L);
+    acc0 += a0 * __ldg(x + c0);
+    acc1 += a1 * __ldg(x + c1);
+  }
+  if (p < e) acc0 += ld_stream(data + p) * __ldg(x + (int64_t)ld_stream(idx + p));
+  V acc = acc0 + acc1;
+#pragma unroll
+  for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+  if (lane == 0 && row < n_rows) y[row] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// stream kernel
+// ---------------------------------------------------------------------------------------------------
+template <typename V>
+struct Wide { typedef double type; };  // accumulator of the long-row pass and of the fix-up
+
+template <typename V, typename I, typename P, int IPT, bool VEC, typename Out>
+__global__ void __launch_bounds__(kThreads)
+spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P* __restrict__ ptr,
+                   const V* __restrict__ x, Out out, const int32_t* __restrict__ tile_row,
+                   V* __restrict__ carry, V* __restrict__ head, int64_t nnz, int lane_shift) {
+  constexpr int T = kThreads * IPT;
+  constexpr int RC = T < 2048 ? T : 2048;  // offsets kept in shared memory per pass: RC + 1
+  constexpr int LONG_CAP = T / 32 + 2;
+  constexpr int NW = kThreads / 32;
+  __shared__ __align__(16) V s_prod[T];
+  __shared__ int32_t s_off[RC + 1];
+  __shared__ int32_t s_long[LONG_CAP];
+  __shared__ int s_nlong;
+  __shared__ int s_head_partial;
+
+  const int tid = threadIdx.x;
+  const int64_t t = blockIdx.x;
+  const int64_t lo = t * (int64_t)T;
+  const int cnt = (int)((nnz - lo) < (int64_t)T ? (nnz - lo) : (int64_t)T);
+  const int32_t ra = tile_row[t];
+  const int32_t rb = tile_row[t + 1];
+
+  // ---- A: products into shared memory ------------------------------------------------------------
+  if (VEC && cnt == T) {
+    V v[IPT];
+    I c[IPT];
+#pragma unroll
+    for (int j = 0; j < IPT / 4; ++j) {
+      const int64_t e = lo + (int64_t)(j * kThreads + tid) * 4;
+      ld_stream4(data + e, *reinterpret_cast<V(*)[4]>(&v[4 * j]));
+      ld_stream4(idx + e, *reinterpret_cast<I(*)[4]>(&c[4 * j]));
+    }
+#pragma unroll
+    for (int k = 0; k < IPT; ++k) v[k] *= __ldg(x + (int64_t)c[k]);
+#pragma unroll
+    for (int j = 0; j < IPT / 4; ++j)
+      st_shared4(&s_prod[(j * kThreads + tid) * 4], *reinterpret_cast<V(*)[4]>(&v[4 * j]));
+  } else {
+    for (int e = tid; e < cnt; e += kThreads)
+      s_prod[e] = ld_stream(data + lo + e) * __ldg(x + (int64_t)ld_stream(idx + lo + e));
+  }
+
+  // ---- B/C: segments = rows ending here (ra..rb-1) + the row that continues (tail) ---------------
+  const int nrf = rb - ra;
+  const int nseg = nrf + 1;
+  int L;
+  {
+    const int mean = cnt / nseg;
+    L = pow2_floor(mean >> lane_shift);
+    L = L > 32 ? 32 : L;
+  }
+  const int lane = tid & (L - 1);
+  const int grp = tid / L;
+  const int ngrp = kThreads / L;
+  const int long_len = 32 * L;
+  typedef typename Wide<V>::type W;
+
+  for (int base = 0; base < nseg; base += RC) {
+    const int m = (nseg - base) < RC ? (nseg - base) : RC;  // segments in this pass
+    __syncthreads();  // products visible; previous pass done with s_off / s_long
+    for (int k = tid; k <= m; k += kThreads) {
+      const int g = base + k;  // offset entry g: start of segment g
+      int32_t o = cnt;         // g == nseg: end of the tail segment
+      if (g <= nrf) {
+        const int64_t d = (int64_t)ptr[(int64_t)ra + g] - lo;
+        o = d < 0 ? 0 : (d > cnt ? cnt : (int32_t)d);
+        if (g == 0) s_head_partial = (d < 0 && nrf > 0) ? 1 : 0;
+      }
+      s_off[k] = o;
+    }
+    if (tid == 0) s_nlong = 0;
+    __syncthreads();
+
+    // pass 1: L lanes per segment
+    const int iters = (m + ngrp - 1) / ngrp;
+    for (int it = 0; it < iters; ++it) {
+      const int k = it * ngrp + grp;
+      const bool valid = k < m;
+      int s = 0, e = 0;
+      if (valid) {
+        s = s_off[k];
+        e = s_off[k + 1];
+      }
+      const bool is_long = (L < 32) && (e - s > long_len);
+      V acc = 0;
+      if (!is_long)
+        for (int p = s + lane; p < e; p += L) acc += s_prod[p];
+      for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+      if (valid && lane == 0) {
+        if (is_long) {
+          s_long[atomicAdd(&s_nlong, 1)] = k;
+        } else {
+          const int g = base + k;
+          if (g == nrf) carry[t] = acc;
+          else if (g == 0 && s_head_partial) head[t] = acc;
+          else out.store((int64_t)ra + g, acc);
+        }
+      }
+    }
+    __syncthreads();
+
+    // pass 2: one warp per long segment, wide accumulators
+    const int nlong = s_nlong;
+    const int w = tid >> 5, l32 = tid & 31;
+    for (int q = w; q < nlong; q += NW) {
+      const int k = s_long[q];
+      const int s = s_off[k], e = s_off[k + 1];
+      W a0 = 0, a1 = 0;
+      int p = s + l32;
+      for (; p + 32 < e; p += 64) {
+        a0 += (W)s_prod[p];
+        a1 += (W)s_prod[p + 32];
+      }
+      if (p < e) a0 += (W)s_prod[p];
+      W acc = a0 + a1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+      if (l32 == 0) {
+        const int g = base + k;
+        if (g == nrf) carry[t] = (V)acc;
+        else if (g == 0 && s_head_partial) head[t] = (V)acc;
+        else out.store((int64_t)ra + g, (V)acc);
+      }
+    }
+  }
+}
+
+// one thread per tile t >= 1: if the first row written by tile t started in an earlier tile, finish it
+template <typename V, typename P, typename Out>
+__global__ void __launch_bounds__(kThreads)
+spmv_fixup_kernel(const P* __restrict__ ptr, const int32_t* __restrict__ tile_row,
+                  const V* __restrict__ carry, const V* __restrict__ head, Out out, int64_t n_tiles,
+                  int log2_tile) {
+  const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x + 1;
+  if (t >= n_tiles) return;
+  const int32_t ra = tile_row[t];
+  const int32_t rb = tile_row[t + 1];
+  if (ra >= rb) return;                       // no row ends in this tile
+  const int64_t p = (int64_t)ptr[ra];
+  if (p >= (t << log2_tile)) return;          // its first row starts inside the tile
+  const int64_t t0 = p >> log2_tile;
+  // Neumaier-compensated sum in double: exact enough for either value type whatever the row length
+  double sum = (double)head[t], comp = 0.0;
+  for (int64_t u = t0; u < t; ++u) {
+    const double v = (double)carry[u];
+    const double s2 = sum + v;
+    comp += (fabs(sum) >= fabs(v)) ? ((sum - s2) + v) : ((v - s2) + sum);
+    sum = s2;
+  }
+  out.store((int64_t)ra, (V)(sum + comp));
+}
+
+template <typename V, typename Out>
+__global__ void __launch_bounds__(kThreads) fill_zero_kernel(Out out, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i < n) out.store(i, (V)0);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host-side dispatch
+// ---------------------------------------------------------------------------------------------------
+static int ipt_of(int tuning) {
+  switch ((tuning >> 8) & 3) {
+    case 1: return 4;
+    case 3: return 16;
+    default: return 8;
+  }
+}
+
+template <typename V, typename I, typename P, int L>
+static void launch_vector(const void* data, const void* idx, const void* ptr, const void* x, void* y,
+                          int64_t n_rows, cudaStream_t st) {
+  const int64_t threads = n_rows * L;
+  const int64_t g = (threads + kThreads - 1) / kThreads;
+  spmv_vector_kernel<V, I, P, L><<<(unsigned)g, kThreads, 0, st>>>((const V*)data, (const I*)idx,
+                                                                   (const P*)ptr, (const V*)x, (V*)y, n_rows);
+}
+
+template <typename V, typename I, typename P>
+static int run_vector(const void* data, const void* idx, const void* ptr, const void* x, void* y,
+                      int64_t n_rows, int64_t nnz, int tuning, cudaStream_t st) {
+  int L = tuning & 0xff;
+  if (L == 0) {
+    const int64_t mean = n_rows > 0 ? nnz / n_rows : 0;
+    L = 2;
+    while (L < 32 && 2 * L <= mean) L <<= 1;  // about two elements per lane
+  }
+  if (n_rows * (int64_t)L / kThreads >= INT32_MAX) return FSB_ERANGE;
+  switch (L) {
+    case 2: launch_vector<V, I, P, 2>(data, idx, ptr, x, y, n_rows, st); break;
+    case 4: launch_vector<V, I, P, 4>(data, idx, ptr, x, y, n_rows, st); break;
+    case 8: launch_vector<V, I, P, 8>(data, idx, ptr, x, y, n_rows, st); break;
+    case 16: launch_vector<V, I, P, 16>(data, idx, ptr, x, y, n_rows, st); break;
+    case 32: launch_vector<V, I, P, 32>(data, idx, ptr, x, y, n_rows, st); break;
+    default: return FSB_EINVAL;
+  }
+  FSB_RETURN_IF_LAUNCH_FAILED();
+  return FSB_OK;
+}
+
+template <typename V, typename I, typename P, int IPT, typename Out>
+static int launch_stream(const void* data, const void* idx, const void* ptr, const void* x, Out out,
+                         const int32_t* tile_row, void* scratch, int64_t nnz, int tuning, cudaStream_t st) {
+  constexpr int T = kThreads * IPT;
+  const int64_t n_tiles = (nnz + T - 1) / T;
+  V* carry = (V*)scratch;
+  V* head = carry + n_tiles;
+  int shift = (tuning & 0xff) ? (tuning & 0xff) - 1 : 2;
+  if (shift > 16) shift = 16;
+  const bool vec = aligned_to(data, 16) && aligned_to(idx, 16);
+  if (vec)
+    spmv_stream_kernel<V, I, P, IPT, true, Out><<<(unsigned)n_tiles, kThreads, 0, st>>>(
+        (const V*)data, (const I*)idx, (const P*)ptr, (const V*)x, out, tile_row, carry, head, nnz, shift);
+  else
+    spmv_stream_kernel<V, I, P, IPT, false, Out><<<(unsigned)n_tiles, kThreads, 0, st>>>(
+        (const V*)data, (const I*)idx, (const P*)ptr, (const V*)x, out, tile_row, carry, head, nnz, shift);
+  FSB_RETURN_IF_LAUNCH_FAILED();
+  if (n_tiles > 1) {
+    int log2_tile = 0;
+    while ((1 << log2_tile) < T) ++log2_tile;
+    const int64_t g = (n_tiles - 1 + kThreads - 1) / kThreads;
+    spmv_fixup_kernel<V, P, Out><<<(unsigned)g, kThreads, 0, st>>>((const P*)ptr, tile_row, carry, head, out,
+                                                                  n_tiles, log2_tile);
+    FSB_RETURN_IF_LAUNCH_FAILED();
+  }
+  return FSB_OK;
+}
+
+template <typename V, typename I, typename P, typename Out>
+static int run_stream(const void* data, const void* idx, const void* ptr, const void* x, Out out,
+                      const int32_t* tile_row, void* scratch, int64_t nnz, int tuning, cudaStream_t st) {
+  switch (ipt_of(tuning)) {
+    case 4: return launch_stream<V, I, P, 4, Out>(data, idx, ptr, x, out, tile_row, scratch, nnz, tuning, st);
+    case 16: return launch_stream<V, I, P, 16, Out>(data, idx, ptr, x, out, tile_row, scratch, nnz, tuning, st);
+    default: return launch_stream<V, I, P, 8, Out>(data, idx, ptr, x, out, tile_row, scratch, nnz, tuning, st);
+  }
+}
+
+struct SpmvArgs {
+  const void *data, *idx, *ptr, *x;
+  void* y;
+  void* const* y_peers;
+  int n_peers;
+  int64_t row_offset, n_rows, nnz;
+  int algo, tuning;
+  const int32_t* tile_row;
+  void* scratch;
+  cudaStream_t st;
+};
+
+template <typename V, typename I, typename P>
+static int spmv_typed(const SpmvArgs& a) {
+  if (a.algo == FSB_SPMV_VECTOR)
+    return run_vector<V, I, P>(a.data, a.idx, a.ptr, a.x, a.y, a.n_rows, a.nnz, a.tuning, a.st);
+  if (a.y_peers) {
+    PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset};
+    return run_stream<V, I, P, PeerOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.tile_row, a.scratch, a.nnz,
+                                           a.tuning, a.st);
+  }
+  LocalOut<V> out{(V*)a.y};
+  return run_stream<V, I, P, LocalOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.tile_row, a.scratch, a.nnz,
+                                          a.tuning, a.st);
+}
+
+static int spmv_dispatch(int vtype, int itype, int ptype, const SpmvArgs& a) {
+#define FSB_CASE(VT, V, IT, I, PT, P) \
+  if (vtype == VT && itype == IT && ptype == PT) return spmv_typed<V, I, P>(a);
+  FSB_CASE(FSB_F32, float, FSB_I32, int32_t, FSB_I32, int32_t)
+  FSB_CASE(FSB_F32, float, FSB_I32, int32_t, FSB_I64, int64_t)
+  FSB_CASE(FSB_F32, float, FSB_I64, int64_t, FSB_I32, int32_t)
+  FSB_CASE(FSB_F32, float, FSB_I64, int64_t, FSB_I64, int64_t)
+  FSB_CASE(FSB_F64, double, FSB_I32, int32_t, FSB_I32, int32_t)
+  FSB_CASE(FSB_F64, double, FSB_I32, int32_t, FSB_I64, int64_t)
+  FSB_CASE(FSB_F64, double, FSB_I64, int64_t, FSB_I32, int32_t)
+  FSB_CASE(FSB_F64, double, FSB_I64, int64_t, FSB_I64, int64_t)
+#undef FSB_CASE
+  return FSB_EINVAL;
+}
+
+static int check_common(int vtype, int itype, int ptype, const void* data, const void* indices,
+                        const void* indptr, const void* x, int64_t n_rows, int64_t n_cols, int64_t nnz) {
+  if ((vtype != FSB_F32 && vtype != FSB_F64) || (itype != FSB_I32 && itype != FSB_I64) ||
+      (ptype != FSB_I32 && ptype != FSB_I64))
+    return FSB_EINVAL;
+  if (n_rows < 0 || n_cols < 0 || nnz < 0) return FSB_EINVAL;
+  if (n_rows >= INT32_MAX || n_cols >= INT32_MAX) return FSB_ERANGE;
+  if (ptype == FSB_I32 && nnz > INT32_MAX) return FSB_ERANGE;
+  if (indptr == nullptr) return FSB_EINVAL;
+  if (nnz > 0 && (data == nullptr || indices == nullptr || x == nullptr)) return FSB_EINVAL;
+  const size_t sv = vtype == FSB_F32 ? 4 : 8, si = itype == FSB_I32 ? 4 : 8, sp = ptype == FSB_I32 ? 4 : 8;
+  if (!aligned_to(data, sv) || !aligned_to(x, sv) || !aligned_to(indices, si) || !aligned_to(indptr, sp))
+    return FSB_EALIGN;
+  return FSB_OK;
+}
+
+}  // namespace fsb
+
+using namespace fsb;
+
+extern "C" int fsb_spmv_tile_nnz(int vtype, int tuning) {
+  (void)vtype;
+  return kThreads * ipt_of(tuning);
+}
+
+extern "C" size_t fsb_spmv_csr_scratch_bytes(int vtype, int64_t nnz, int tuning) {
+  const int T = fsb_spmv_tile_nnz(vtype, tuning);
+  const int64_t n_tiles = fsb_csr_num_tiles(nnz, T);
+  const size_t sv = vtype == FSB_F32 ? 4 : 8;
+  size_t b = (size_t)n_tiles * 2 * sv;
+  return (b + 255) & ~(size_t)255;
+}
+
+extern "C" int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, const void* indices,
+                            const void* indptr, const void* x, void* y, int64_t n_rows, int64_t n_cols,
+                            int64_t nnz, int algo, int tuning, const int32_t* tile_row, void* scratch,
+                            size_t scratch_bytes, void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
+  if (rc != FSB_OK) return rc;
+  if (n_rows == 0) return FSB_OK;
+  if (y == nullptr) return FSB_EINVAL;
+  const size_t sv = vtype == FSB_F32 ? 4 : 8;
+  if (!aligned_to(y, sv)) return FSB_EALIGN;
+  if (nnz == 0) return cuda_rc(cudaMemsetAsync(y, 0, (size_t)n_rows * sv, st));
+  if (algo == FSB_SPMV_AUTO)
+    algo = (tile_row != nullptr && scratch != nullptr && nnz >= (1 << 20)) ? FSB_SPMV_STREAM : FSB_SPMV_VECTOR;
+  if (algo != FSB_SPMV_VECTOR && algo != FSB_SPMV_STREAM) return FSB_EINVAL;
+  if (algo == FSB_SPMV_STREAM) {
+    if (tile_row == nullptr || scratch == nullptr) return FSB_EINVAL;
+    if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
+    if (!aligned_to(scratch, 16)) return FSB_EALIGN;
+  }
+  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, n_rows, nnz, algo, tuning, tile_row, scratch, st};
+  return spmv_dispatch(vtype, itype, ptype, a);
+}
+
+extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
+                                    const void* indptr, const void* x, void* const* y_peers, int n_peers,
+                                    int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                                    int tuning, const int32_t* tile_row, void* scratch, size_t scratch_bytes,
+                                    void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
+  if (rc != FSB_OK) return rc;
+  if (y_peers == nullptr || n_peers < 1 || n_peers > 64 || row_offset < 0) return FSB_EINVAL;
+  if (n_rows == 0) return FSB_OK;
+  if (nnz == 0) {
+    const unsigned g = (unsigned)((n_rows + kThreads - 1) / kThreads);
+    if (vtype == FSB_F32)
+      fill_zero_kernel<float, PeerOut<float>><<<g, kThreads, 0, st>>>(
+          PeerOut<float>{(float* const*)y_peers, n_peers, row_offset}, n_rows);
+    else
+      fill_zero_kernel<double, PeerOut<double>><<<g, kThreads, 0, st>>>(
+          PeerOut<double>{(double* const*)y_peers, n_peers, row_offset}, n_rows);
+    FSB_RETURN_IF_LAUNCH_FAILED();
+    return FSB_OK;
+  }
+  if (tile_row == nullptr || scratch == nullptr) return FSB_EINVAL;
+  if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
+  if (!aligned_to(scratch, 16)) return FSB_EALIGN;
+  SpmvArgs a{data, indices, indptr, x, nullptr, y_peers, n_peers, row_offset, n_rows, nnz,
+             FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
+  return spmv_dispatch(vtype, itype, ptype, a);
+}

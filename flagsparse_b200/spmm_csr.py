@@ -1,0 +1,332 @@
+"""CSR SpMM host code: the reference's entry points over the hand-written sm_100a kernel.
+
+Same names, arguments, defaults, validation order and exception types as the reference's
+src/flagsparse/sparse_operations/spmm_csr.py (_prepare_spmm_csr_matrix :197-255,
+_prepare_spmm_csr_inputs :258-281, _resolve_spmm_alg1_launch_config :284-334, PreparedCsrSpmmOpt
+:337-392, prepare_spmm_csr_opt :480-522, flagsparse_spmm_csr :1057-1126, flagsparse_spmm_csr_opt
+:1129-1183).  Both entry points run the same nnz-tiled CUDA kernel; the reference's row-length buckets
+and its split workspace for rows over 2048 nnz are replaced by the tile plan and per-tile partial rows.
+"""
+
+import os
+import time
+
+import torch
+
+from . import _lib
+from ._common import (
+    SUPPORTED_INDEX_DTYPES,
+    _INDEX_LIMIT_INT32,
+    _ITYPE,
+    _VTYPE,
+    _analyze_csr,
+    _check_value_dtype,
+    _ptr,
+    _stream_ptr,
+    _tile_plan,
+)
+
+_SPMM_ALGO_NAMES = {"auto": _lib.FSB_SPMM_AUTO, "plain": _lib.FSB_SPMM_PLAIN, "bulk": _lib.FSB_SPMM_BULK}
+
+
+def _prepare_spmm_csr_matrix(data, indices, indptr, shape):
+    """Checks of the reference's function of this name (spmm_csr.py:197-255), in its order.  Returns
+    (data, kernel_indices, kernel_indptr, n_rows, n_cols, stats); unlike the reference the indptr keeps
+    its 32-bit width when it has one (the kernels read either)."""
+    if len(shape) != 2:
+        raise ValueError("shape must be a 2-tuple: (n_rows, n_cols)")
+    if data.ndim != 1 or indices.ndim != 1 or indptr.ndim != 1:
+        raise ValueError("data, indices, and indptr must be 1D tensors")
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    if n_rows < 0 or n_cols < 0:
+        raise ValueError("shape dimensions must be non-negative")
+    if indptr.numel() != n_rows + 1:
+        raise ValueError(f"indptr length must be n_rows+1={n_rows + 1}, got {indptr.numel()}")
+    if data.numel() != indices.numel():
+        raise ValueError("data and indices must have the same length (nnz)")
+    if not all(t.is_cuda for t in (data, indices, indptr)):
+        raise ValueError("data, indices, and indptr must be CUDA tensors")
+    if not all(t.device == data.device for t in (indices, indptr)):
+        raise ValueError("data, indices, and indptr must be on the same CUDA device")
+    _check_value_dtype(data.dtype)
+    if indices.dtype not in SUPPORTED_INDEX_DTYPES:
+        raise TypeError("indices dtype must be torch.int32 or torch.int64")
+    if indptr.dtype not in SUPPORTED_INDEX_DTYPES:
+        raise TypeError("indptr dtype must be torch.int32 or torch.int64")
+
+    data = data.contiguous()
+    indices = indices.contiguous()
+    indptr = indptr.contiguous()
+    nnz = data.numel()
+    stats = _analyze_csr(indices, indptr, n_rows)
+    if stats.ptr_first != 0:
+        raise ValueError("indptr[0] must be 0")
+    if stats.ptr_last != nnz:
+        raise ValueError(f"indptr[-1] must equal nnz={nnz}, got {stats.ptr_last}")
+    if stats.n_decreasing > 0:
+        raise ValueError("indptr must be nondecreasing")
+    if nnz > 0:
+        if stats.min_index < 0 or stats.max_index >= n_cols:
+            raise IndexError("indices out of range for n_cols")
+        if stats.max_index > _INDEX_LIMIT_INT32:
+            raise ValueError("column indices exceed the int32 range supported by the kernel")
+    kernel_indices = indices.to(torch.int32) if indices.dtype == torch.int64 else indices
+    return data, kernel_indices, indptr, n_rows, n_cols, stats
+
+
+def _check_spmm_dense(B, data, n_cols):
+    """Checks on B of the reference's _prepare_spmm_csr_inputs (spmm_csr.py:271-280)."""
+    if B.shape[0] != n_cols:
+        raise ValueError(f"B.shape[0] must be n_cols={n_cols}, got {B.shape[0]}")
+    if not B.is_cuda:
+        raise ValueError("B must be a CUDA tensor")
+    if B.device != data.device:
+        raise ValueError("B must be on the same CUDA device as the sparse matrix")
+    if B.dtype != data.dtype:
+        raise TypeError("B dtype must match data dtype")
+    return B.contiguous()
+
+
+def _select_spmm_alg1_warp_and_factor(n_dense_cols):
+    """Tile-shape table of the reference (spmm_csr.py:284-296)."""
+    if n_dense_cols > 64:
+        return 32, 4
+    if n_dense_cols > 32:
+        return 32, 2
+    if n_dense_cols > 16:
+        return 32, 1
+    if n_dense_cols > 8:
+        return 16, 1
+    if n_dense_cols > 4:
+        return 8, 1
+    return 4, 1
+
+
+def _resolve_spmm_alg1_launch_config(n_dense_cols, max_row_nnz, block_n=None, block_nnz=None, max_segments=None):
+    """Validate the launch overrides the way the reference does (spmm_csr.py:299-334).  The CUDA kernel
+    ignores the resulting numbers; the function exists so that bad overrides raise the same ValueError,
+    including the one for a max_segments too small for the longest row."""
+    warp_size, factor = _select_spmm_alg1_warp_and_factor(n_dense_cols)
+    if block_n is None:
+        block_n = warp_size * factor
+    if block_nnz is None:
+        block_nnz = warp_size
+    if block_n <= 0 or block_nnz <= 0:
+        raise ValueError("block_n and block_nnz must be positive when provided")
+    if max_segments is not None and max_segments <= 0:
+        raise ValueError("max_segments must be positive when provided")
+    required_segments = -(-max_row_nnz // block_nnz) if max_row_nnz > 0 else 0
+    if max_segments is not None and required_segments > int(max_segments):
+        raise ValueError(
+            "row nnz requires more CSR segments than the explicit max_segments override allows: "
+            f"required {required_segments}, provided {int(max_segments)}"
+        )
+    return {
+        "block_n": int(block_n),
+        "block_nnz": int(block_nnz),
+        "max_segments": (None if max_segments is None else int(max_segments)),
+        "required_segments": int(required_segments),
+        "warp_size": int(warp_size),
+        "factor": int(factor),
+        "max_row_nnz": int(max_row_nnz),
+        "auto_max_segments": max_segments is None,
+    }
+
+
+def _select_spmm_opt_block_n(n_dense_cols):
+    """Column-tile table of the reference's opt path (spmm_csr.py:405-414); informational here."""
+    for bound in (8, 16, 32, 64):
+        if n_dense_cols <= bound:
+            return bound
+    return 128
+
+
+class PreparedCsrSpmmOpt:
+    """Cached CSR metadata for repeated SpMM calls on the same sparse matrix.
+
+    Attribute names follow the reference's class (spmm_csr.py:337-392).  `row_buckets` describes the tile
+    plan; the `long_*` split tables of the reference stay empty because rows of any length go through the
+    same tiles.  Scratch (two partial rows per tile) depends on the width of B and is cached per width:
+    calls that share a prepared object must not overlap on the GPU.
+    """
+
+    __slots__ = (
+        "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "max_row_nnz",
+        "row_buckets", "supports_opt", "long_part_rows", "long_part_starts", "long_part_ends",
+        "long_row_ids", "long_row_part_ptr", "long_row_fallback_only", "stats", "tile_nnz", "tile_row",
+        "_scratch", "_status", "_row_lengths",
+    )
+
+    def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, tile_nnz, tile_row):
+        dev = data.device
+        self.data = data
+        self.kernel_indices = kernel_indices
+        self.kernel_indptr = kernel_indptr
+        self.shape = (int(shape[0]), int(shape[1]))
+        self.n_rows = int(n_rows)
+        self.n_cols = int(n_cols)
+        self.max_row_nnz = int(stats.max_row_nnz)
+        self.stats = stats
+        self.tile_nnz = tile_nnz
+        self.tile_row = tile_row
+        n_tiles = 0 if tile_row is None else tile_row.numel() - 1
+        self.row_buckets = [{"kind": "tiles", "tile_nnz": tile_nnz, "n_tiles": n_tiles, "n_rows": self.n_rows}]
+        self.supports_opt = data.dtype in (torch.float32, torch.float64)
+        self.long_part_rows = torch.empty((0,), dtype=torch.int32, device=dev)
+        self.long_part_starts = torch.empty((0,), dtype=torch.int64, device=dev)
+        self.long_part_ends = torch.empty((0,), dtype=torch.int64, device=dev)
+        self.long_row_ids = torch.empty((0,), dtype=torch.int32, device=dev)
+        self.long_row_part_ptr = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.long_row_fallback_only = False
+        self._scratch = {}
+        self._status = None
+        self._row_lengths = None
+
+    @property
+    def row_lengths(self):
+        if self._row_lengths is None:
+            p = self.kernel_indptr.to(torch.int64)
+            self._row_lengths = p[1:] - p[:-1] if self.n_rows > 0 else p.new_empty((0,))
+        return self._row_lengths
+
+    def scratch_for(self, n_dense):
+        buf = self._scratch.get(n_dense)
+        if buf is None:
+            nbytes = int(_lib.lib().fsb_spmm_csr_scratch_bytes(_VTYPE[self.data.dtype], self.data.numel(), n_dense))
+            buf = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.data.device)
+            self._scratch = {n_dense: buf}  # keep one width at a time
+        return buf
+
+    def status_word(self):
+        if self._status is None:
+            self._status = torch.zeros(1, dtype=torch.int32, device=self.data.device)
+        return self._status
+
+
+def prepare_spmm_csr_opt(data, indices, indptr, shape):
+    """Analyse a CSR matrix once for repeated SpMM calls (reference: spmm_csr.py:480-522)."""
+    data, kernel_indices, kernel_indptr, n_rows, n_cols, stats = _prepare_spmm_csr_matrix(
+        data, indices, indptr, shape
+    )
+    nnz = data.numel()
+    tile_nnz, tile_row = 0, None
+    if nnz > 0 and n_rows > 0:
+        tile_nnz = int(_lib.lib().fsb_spmm_tile_nnz(_VTYPE[data.dtype]))
+        tile_row = _tile_plan(kernel_indptr, n_rows, nnz, tile_nnz)
+    return PreparedCsrSpmmOpt(data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, tile_nnz, tile_row)
+
+
+def _spmm_launch(prepared, B, C):
+    """Enqueue C = A B on the current stream.  Stands in for _triton_spmm_csr_impl (spmm_csr.py:525-599)
+    and _triton_spmm_csr_impl_opt_prepared (:1033-1055)."""
+    L = _lib.lib()
+    p = prepared
+    dev = p.data.device
+    n_dense = int(B.shape[1])
+    if p.n_rows == 0 or n_dense == 0:
+        return
+    algo = _SPMM_ALGO_NAMES.get(os.environ.get("FSB_SPMM_ALGO", "auto").strip().lower(), _lib.FSB_SPMM_AUTO)
+    scratch = p.scratch_for(n_dense) if p.tile_row is not None else None
+    with torch.cuda.device(dev):
+        rc = L.fsb_spmm_csr(
+            _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
+            _ptr(p.data), _ptr(p.kernel_indices), p.kernel_indptr.data_ptr(), _ptr(B), B.stride(0),
+            C.data_ptr(), C.stride(0), p.n_rows, p.n_cols, n_dense, p.data.numel(), algo,
+            None if p.tile_row is None else p.tile_row.data_ptr(),
+            None if scratch is None else scratch.data_ptr(), 0 if scratch is None else scratch.numel(),
+            p.status_word().data_ptr(), _stream_ptr(dev),
+        )
+    _lib.check(rc, "fsb_spmm_csr")
+
+
+def _check_out(out, device, shape, dtype, device_msg):
+    if not out.is_cuda:
+        raise ValueError("out must be a CUDA tensor")
+    if out.device != device:
+        raise ValueError(device_msg)
+    if out.shape != shape or out.dtype != dtype:
+        raise ValueError("out shape/dtype must match result")
+
+
+def _run_spmm(prepared, B, out, return_time):
+    dev, dtype = prepared.data.device, prepared.data.dtype
+    shape = (prepared.n_rows, int(B.shape[1]))
+    direct = out is not None and out.is_contiguous()
+    C = out if direct else torch.empty(shape, dtype=dtype, device=dev)
+    t0 = None
+    if return_time:
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+    _spmm_launch(prepared, B, C)
+    elapsed_ms = None
+    if return_time:
+        torch.cuda.synchronize(dev)
+        elapsed_ms = (time.perf_counter() - t0) * 1000.0
+    if out is not None and not direct:
+        out.copy_(C)
+        C = out
+    if return_time:
+        return C, elapsed_ms
+    return C
+
+
+def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz=None, max_segments=None,
+                        out=None, return_time=False):
+    """CSR SpMM: C = A @ B (reference: spmm_csr.py:1057-1126, same arguments and defaults).
+
+    A is given as CSR arrays; B is a dense CUDA tensor of shape (n_cols, n_dense_cols), any strides.
+    block_n / block_nnz / max_segments are the reference's Triton launch overrides: validated the same
+    way, otherwise unused.  Unlike the reference this call does not synchronise the device unless
+    return_time is set.
+    """
+    if block_n is not None and block_n <= 0:
+        raise ValueError("block_n must be positive when provided")
+    if block_nnz is not None and block_nnz <= 0:
+        raise ValueError("block_nnz must be positive when provided")
+    if max_segments is not None and max_segments <= 0:
+        raise ValueError("max_segments must be positive when provided")
+    if B.ndim != 2:
+        raise ValueError("B must be a 2D dense tensor")
+    prepared = prepare_spmm_csr_opt(data, indices, indptr, shape)
+    B = _check_spmm_dense(B, prepared.data, prepared.n_cols)
+    n_dense_cols = int(B.shape[1])
+    _resolve_spmm_alg1_launch_config(n_dense_cols, prepared.max_row_nnz, block_n=block_n, block_nnz=block_nnz,
+                                     max_segments=max_segments)
+    if out is not None:
+        _check_out(out, prepared.data.device, (prepared.n_rows, n_dense_cols), prepared.data.dtype,
+                   "out must be on the same CUDA device as the inputs")
+    return _run_spmm(prepared, B, out, return_time)
+
+
+def flagsparse_spmm_csr_opt(data=None, indices=None, indptr=None, B=None, shape=None, prepared=None, out=None,
+                            return_time=False):
+    """CSR SpMM on a prepared matrix (reference: spmm_csr.py:1129-1183, same arguments and defaults)."""
+    if prepared is not None and not isinstance(prepared, PreparedCsrSpmmOpt):
+        raise TypeError("prepared must be a PreparedCsrSpmmOpt instance")
+    if prepared is None:
+        if any(arg is None for arg in (data, indices, indptr, shape)):
+            raise ValueError("data, indices, indptr, and shape are required when prepared is not provided")
+        prepared = prepare_spmm_csr_opt(data, indices, indptr, shape)
+    elif shape is not None:
+        resolved_shape = (int(shape[0]), int(shape[1]))
+        if resolved_shape != prepared.shape:
+            raise ValueError(f"shape {resolved_shape} does not match prepared.shape {prepared.shape}")
+    if B is None:
+        raise ValueError("B is required")
+    if not prepared.supports_opt:
+        raise TypeError("flagsparse_spmm_csr_opt only supports float32 and float64")
+    if not B.is_cuda:
+        raise ValueError("B must be a CUDA tensor")
+    if B.device != prepared.data.device:
+        raise ValueError("B must be on the same CUDA device as sparse matrix data")
+    if out is not None:
+        _check_out(out, prepared.data.device, (prepared.n_rows, int(B.shape[1])), prepared.data.dtype,
+                   "out must be on the same CUDA device as sparse matrix data")
+    # checks the reference makes inside its launch helper (:1040-1046)
+    if B.dtype != prepared.data.dtype:
+        raise TypeError("B dtype must match sparse matrix dtype")
+    if B.shape[0] != prepared.n_cols:
+        raise ValueError(f"B.shape[0] must be n_cols={prepared.n_cols}, got {B.shape[0]}")
+    if B.ndim != 2:
+        raise ValueError("B must be a 2D dense tensor")
+    return _run_spmm(prepared, B.contiguous(), out, return_time)

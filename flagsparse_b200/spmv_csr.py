@@ -1,0 +1,318 @@
+"""CSR SpMV host code: the reference's entry points over hand-written sm_100a kernels.
+
+Same names, arguments, defaults, validation order and exception types as the reference's
+src/flagsparse/sparse_operations/spmv_csr.py (PreparedCsrSpmv :9-58, _prepare_spmv_csr_matrix :379-436,
+_validate_spmv_x :439-452, prepare_spmv_csr :455-495, flagsparse_spmv_csr :557-610, the COO front-end
+:613-758).  What differs is below the boundary: one fused analysis pass instead of six reductions, an
+nnz-tile plan instead of row-length buckets, and CUDA kernels (libfsb.so) instead of Triton launches.
+"""
+
+import os
+import time
+
+import torch
+
+from . import _lib
+from ._common import (
+    SUPPORTED_INDEX_DTYPES,
+    _INDEX_LIMIT_INT32,
+    _ITYPE,
+    _VTYPE,
+    _analyze_csr,
+    _check_value_dtype,
+    _ptr,
+    _stream_ptr,
+    _tile_plan,
+)
+
+# matrices below this many nnz are a handful of tiles: the single-launch vector kernel wins on latency
+_STREAM_MIN_NNZ = 1 << 18
+# the vector kernel gives a row to at most 32 lanes, so it is kept away from very long rows
+_VECTOR_MAX_ROW_NNZ = 4096
+
+_ALGO_NAMES = {"auto": _lib.FSB_SPMV_AUTO, "vector": _lib.FSB_SPMV_VECTOR, "stream": _lib.FSB_SPMV_STREAM}
+
+
+def _resolve_block_nnz(max_row_nnz, block_nnz, max_segments):
+    """block_nnz / max_segments bookkeeping of the reference (spmv_csr.py:465-475).  The CUDA kernels do
+    not use either number; they are kept as attributes of the prepared object."""
+    block_nnz_use = block_nnz
+    if max_segments is None:
+        max_segments_use = max((max_row_nnz + block_nnz_use - 1) // block_nnz_use, 1)
+        while max_segments_use > 2048 and block_nnz_use < 65536:
+            block_nnz_use *= 2
+            max_segments_use = max((max_row_nnz + block_nnz_use - 1) // block_nnz_use, 1)
+    else:
+        max_segments_use = max_segments
+    return block_nnz_use, max_segments_use
+
+
+def _select_spmv_algo(n_rows, nnz, max_row_nnz):
+    """Kernel choice from indptr statistics: the nnz-tiled stream kernel whenever the matrix is big
+    enough to fill the GPU or has long rows, else the lanes-per-row vector kernel."""
+    forced = os.environ.get("FSB_SPMV_ALGO", "").strip().lower()
+    if forced in ("vector", "stream"):
+        return _ALGO_NAMES[forced]
+    if nnz < _STREAM_MIN_NNZ and max_row_nnz <= _VECTOR_MAX_ROW_NNZ:
+        return _lib.FSB_SPMV_VECTOR
+    return _lib.FSB_SPMV_STREAM
+
+
+class PreparedCsrSpmv:
+    """Cached CSR metadata for repeated SpMV calls on the same sparse matrix.
+
+    Carries the attributes of the reference's class (spmv_csr.py:9-58) plus the tile plan and scratch of
+    the stream kernel.  `opt_buckets` describes the plan (the reference lists row ids per length bucket
+    there).  One prepared object owns one scratch buffer: calls that share it must not overlap on the GPU.
+    """
+
+    __slots__ = (
+        "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "block_nnz",
+        "max_segments", "max_row_nnz", "opt_buckets", "supports_opt", "stats", "algo", "tuning",
+        "tile_nnz", "tile_row", "scratch",
+    )
+
+    def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
+                 max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch):
+        self.data = data
+        self.kernel_indices = kernel_indices
+        self.kernel_indptr = kernel_indptr
+        self.shape = (int(shape[0]), int(shape[1]))
+        self.n_rows = n_rows
+        self.n_cols = n_cols
+        self.block_nnz = block_nnz
+        self.max_segments = max_segments
+        self.max_row_nnz = max_row_nnz
+        self.supports_opt = data.dtype in (torch.float32, torch.float64)
+        self.stats = stats
+        self.algo = algo
+        self.tuning = tuning
+        self.tile_nnz = tile_nnz
+        self.tile_row = tile_row
+        self.scratch = scratch
+        n_tiles = 0 if tile_row is None else tile_row.numel() - 1
+        self.opt_buckets = [
+            {"kind": "stream" if algo == _lib.FSB_SPMV_STREAM else "vector", "tile_nnz": tile_nnz,
+             "n_tiles": n_tiles, "n_rows": n_rows}
+        ]
+
+
+def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
+    """Validate and normalise the CSR arrays; same checks, order and exception types as the reference's
+    function of this name (spmv_csr.py:379-436).  Returns (data, kernel_indices, kernel_indptr, n_rows,
+    n_cols, stats)."""
+    if not all(torch.is_tensor(t) for t in (data, indices, indptr)):
+        raise TypeError("data, indices, indptr must all be torch.Tensor")
+    if data.ndim != 1 or indices.ndim != 1 or indptr.ndim != 1:
+        raise ValueError("data, indices, indptr must be 1D tensors")
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    if indptr.numel() != n_rows + 1:
+        raise ValueError(f"indptr length must be n_rows+1={n_rows + 1}, got {indptr.numel()}")
+    if data.numel() != indices.numel():
+        raise ValueError("data and indices must have the same length (nnz)")
+    if not all(t.is_cuda for t in (data, indices, indptr)):
+        raise ValueError("data, indices, indptr must be CUDA tensors")
+    _check_value_dtype(data.dtype)
+    if indices.dtype not in SUPPORTED_INDEX_DTYPES:
+        raise TypeError("indices dtype must be torch.int32 or torch.int64")
+
+    data = data.contiguous()
+    indices = indices.contiguous()
+    indptr = indptr.contiguous()
+    if indptr.dtype not in SUPPORTED_INDEX_DTYPES:
+        # the reference accepts any integer indptr and converts it (:423-425)
+        indptr = indptr.to(torch.int64)
+
+    nnz = data.numel()
+    stats = _analyze_csr(indices, indptr, n_rows)
+    if stats.ptr_first != 0:
+        raise ValueError("indptr must start at zero")
+    if stats.ptr_last != nnz:
+        raise ValueError("indptr[-1] must equal nnz")
+    if stats.n_decreasing > 0:
+        raise ValueError("indptr must be non-decreasing")
+    if nnz > 0:
+        if stats.min_index < 0 or stats.max_index >= n_cols:
+            raise IndexError("indices out of range for n_cols")
+        if stats.max_index > _INDEX_LIMIT_INT32:
+            raise ValueError(f"int64 column index {stats.max_index} exceeds the int32 kernel range")
+    # same narrowing as the reference (:422-425): 32-bit column indices always, 32-bit indptr when it fits
+    kernel_indices = indices.to(torch.int32) if indices.dtype == torch.int64 else indices
+    kernel_indptr = indptr.to(torch.int32) if nnz <= _INDEX_LIMIT_INT32 else indptr.to(torch.int64)
+    return data, kernel_indices, kernel_indptr, n_rows, n_cols, stats
+
+
+def _validate_spmv_x(x, prepared):
+    """Checks of the reference's _validate_spmv_x (spmv_csr.py:439-452), same order."""
+    if x is None or not torch.is_tensor(x):
+        raise TypeError("x must be a torch.Tensor")
+    if x.ndim != 1:
+        raise ValueError("x must be a 1D tensor")
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor")
+    if x.dtype != prepared.data.dtype:
+        raise TypeError("x dtype must match sparse matrix dtype")
+    if x.numel() != prepared.n_cols:
+        raise ValueError(f"x length must be n_cols={prepared.n_cols}, got {x.numel()}")
+    if x.device != prepared.data.device:
+        raise ValueError("x must be on the same device as sparse matrix data")
+    return x.contiguous()
+
+
+def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=None):
+    """Analyse a CSR matrix once for repeated SpMV calls (reference: spmv_csr.py:455-495)."""
+    data, kernel_indices, kernel_indptr, n_rows, n_cols, stats = _prepare_spmv_csr_matrix(
+        data, indices, indptr, shape
+    )
+    max_row_nnz = stats.max_row_nnz
+    block_nnz_use, max_segments_use = _resolve_block_nnz(max_row_nnz, block_nnz, max_segments)
+    nnz = data.numel()
+    algo = _select_spmv_algo(n_rows, nnz, max_row_nnz)
+    tuning = int(os.environ.get("FSB_SPMV_TUNING", "0"))
+    tile_nnz, tile_row, scratch = 0, None, None
+    if algo == _lib.FSB_SPMV_STREAM and nnz > 0 and n_rows > 0:
+        L = _lib.lib()
+        vt = _VTYPE[data.dtype]
+        tile_nnz = int(L.fsb_spmv_tile_nnz(vt, tuning))
+        tile_row = _tile_plan(kernel_indptr, n_rows, nnz, tile_nnz)
+        scratch = torch.empty(int(L.fsb_spmv_csr_scratch_bytes(vt, nnz, tuning)), dtype=torch.uint8,
+                              device=data.device)
+    return PreparedCsrSpmv(
+        data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape, n_rows=n_rows,
+        n_cols=n_cols, block_nnz=block_nnz_use, max_segments=max_segments_use, max_row_nnz=max_row_nnz,
+        stats=stats, algo=algo, tuning=tuning, tile_nnz=tile_nnz, tile_row=tile_row, scratch=scratch,
+    )
+
+
+def _spmv_launch(prepared, x, y):
+    """Enqueue y = A x on the current stream of the matrix's device.  Stands in for both of the
+    reference's launch helpers (_triton_spmv_csr_impl_opt_prepared :329-376 and
+    _triton_spmv_csr_impl_prepared :510-554): float32 and float64 accumulate natively either way."""
+    L = _lib.lib()
+    p = prepared
+    dev = p.data.device
+    algo = p.algo if p.tile_row is not None else _lib.FSB_SPMV_VECTOR
+    tuning = p.tuning if algo == _lib.FSB_SPMV_STREAM else (p.tuning & 0xFF if p.tuning & 0xFF in (2, 4, 8, 16, 32) else 0)
+    with torch.cuda.device(dev):
+        rc = L.fsb_spmv_csr(
+            _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
+            _ptr(p.data), _ptr(p.kernel_indices), p.kernel_indptr.data_ptr(), _ptr(x), _ptr(y),
+            p.n_rows, p.n_cols, p.data.numel(), algo, tuning,
+            None if p.tile_row is None else p.tile_row.data_ptr(),
+            None if p.scratch is None else p.scratch.data_ptr(),
+            0 if p.scratch is None else p.scratch.numel(), _stream_ptr(dev),
+        )
+    _lib.check(rc, "fsb_spmv_csr")
+
+
+def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None, block_nnz=256,
+                        max_segments=None, out=None, return_time=False, use_opt=False, prepared=None):
+    """CSR SpMV: y = A @ x (reference: spmv_csr.py:557-610, same arguments and defaults).
+
+    data, indices, indptr: CSR arrays; x: dense vector; shape: (n_rows, n_cols).
+    prepared: result of prepare_spmv_csr for steady-state calls.  block_nnz, max_segments and use_opt
+    select Triton launch shapes in the reference; here they are validated bookkeeping only -- both
+    settings of use_opt run the same CUDA kernels.  Returns a new tensor, or `out` when it is given.
+    """
+    if prepared is None:
+        if any(arg is None for arg in (data, indices, indptr, shape)):
+            raise ValueError("data, indices, indptr, and shape are required when prepared is not provided")
+        prepared = prepare_spmv_csr(data, indices, indptr, shape, block_nnz=block_nnz, max_segments=max_segments)
+    x = _validate_spmv_x(x, prepared)
+    dev = prepared.data.device
+    dtype = prepared.data.dtype
+    if out is not None and (out.shape != (prepared.n_rows,) or out.dtype != dtype):
+        raise ValueError("out shape/dtype must match result")
+    # write straight into `out` when that is safe, else into a fresh vector that is copied over
+    direct = out is not None and out.is_cuda and out.device == dev and out.is_contiguous()
+    y = out if direct else torch.empty(prepared.n_rows, dtype=dtype, device=dev)
+    t0 = None
+    if return_time:
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+    _spmv_launch(prepared, x, y)
+    elapsed_ms = None
+    if return_time:
+        torch.cuda.synchronize(dev)
+        elapsed_ms = (time.perf_counter() - t0) * 1000.0
+    if out is not None and not direct:
+        out.copy_(y)
+        y = out
+    if return_time:
+        return y, elapsed_ms
+    return y
+
+
+# ---------------------------------------------------------------------------------------------------
+# COO front-end: convert to CSR, then the same kernels (reference: spmv_csr.py:613-758)
+# ---------------------------------------------------------------------------------------------------
+def _coo_is_sorted_lex(row_i64, col_i64, n_cols):
+    """True iff the COO entries are in non-decreasing (row, col) order (reference :613-620)."""
+    n = row_i64.numel()
+    if n <= 1:
+        return True
+    key = row_i64 * max(1, int(n_cols)) + col_i64
+    return bool((key[1:] >= key[:-1]).all().item())
+
+
+def coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=False):
+    """COO -> (data, int32 column indices, int64 indptr), sorting by (row, col) when needed
+    (reference :623-647)."""
+    n_rows, n_cols = int(shape[0]), int(shape[1])
+    row64 = row.to(torch.int64)
+    col64 = col.to(torch.int64)
+    if row64.numel() == 0:
+        return data, col64.to(torch.int32), torch.zeros(n_rows + 1, dtype=torch.int64, device=data.device)
+    if assume_sorted or _coo_is_sorted_lex(row64, col64, n_cols):
+        row_s, col_s, data_s = row64, col64, data
+    else:
+        order = torch.argsort(row64 * max(1, n_cols) + col64)
+        row_s, col_s, data_s = row64[order], col64[order], data[order]
+    indptr = torch.zeros(n_rows + 1, dtype=torch.int64, device=data.device)
+    indptr[1:] = torch.cumsum(torch.bincount(row_s, minlength=n_rows), dim=0)
+    return data_s, col_s.to(torch.int32), indptr
+
+
+def _check_coo_triple(data, row, col, extra=()):
+    names = "data, row, col" + (", x" if extra else "")
+    tensors = (data, row, col) + tuple(extra)
+    if not all(torch.is_tensor(t) for t in tensors):
+        raise TypeError(f"{names} must all be torch.Tensor")
+    if not all(t.is_cuda for t in tensors):
+        raise ValueError(f"{names} must all be CUDA tensors")
+    if any(t.ndim != 1 for t in tensors):
+        raise ValueError(f"{names} must all be 1D tensors")
+
+
+def prepare_spmv_coo_tocsr(data, row, col, shape, block_nnz=256, max_segments=None, assume_sorted=False):
+    """One-time COO -> CSR + analysis; use with flagsparse_spmv_coo_tocsr(..., prepared=p)
+    (reference :650-684)."""
+    _check_coo_triple(data, row, col)
+    _check_value_dtype(data.dtype)
+    if row.numel() != col.numel() or data.numel() != row.numel():
+        raise ValueError("data, row, col must have the same length")
+    data_s, indices, indptr = coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=assume_sorted)
+    return prepare_spmv_csr(data_s, indices, indptr, shape, block_nnz=block_nnz, max_segments=max_segments)
+
+
+def flagsparse_spmv_coo_tocsr(data=None, row=None, col=None, x=None, shape=None, block_nnz=256,
+                              max_segments=None, out=None, return_time=False, use_opt=True, prepared=None,
+                              assume_sorted=False):
+    """COO SpMV via CSR conversion: y = A @ x (reference :687-758, same arguments and defaults)."""
+    if prepared is not None:
+        if x is None:
+            raise TypeError("x is required")
+        if shape is None:
+            shape = prepared.shape
+        sh = (int(shape[0]), int(shape[1]))
+        if sh != prepared.shape:
+            raise ValueError(f"shape {sh} does not match prepared.shape {prepared.shape}")
+        return flagsparse_spmv_csr(x=x, shape=shape, block_nnz=block_nnz, max_segments=max_segments, out=out,
+                                   return_time=return_time, use_opt=use_opt, prepared=prepared)
+    _check_coo_triple(data, row, col, extra=(x,))
+    _check_value_dtype(data.dtype)
+    if x.dtype != data.dtype:
+        raise TypeError("x dtype must match data dtype")
+    data_s, indices, indptr = coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=assume_sorted)
+    return flagsparse_spmv_csr(data_s, indices, indptr, x, shape, block_nnz=block_nnz,
+                               max_segments=max_segments, out=out, return_time=return_time, use_opt=use_opt)

@@ -1,0 +1,141 @@
+/*
+ * fsb.h -- C ABI of libfsb.so, the sm_100a CUDA library behind flagsparse_b200.
+ *
+ * The reference package (zyq1105331849/flagsparse) has no C/FFI layer: its CSR SpMV and CSR SpMM are
+ * Python functions that launch Triton kernels.  Each entry point below replaces one of those launch sites;
+ * the comment on each names the reference function it stands in for (paths are relative to the reference
+ * project root).  The Python host code in flagsparse_b200/ validates arguments exactly where the reference
+ * does and then calls these functions through ctypes with raw device pointers.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host".
+ *   - vtype: value dtype of data / x / B / y / C.  itype: dtype of `indices`.  ptype: dtype of `indptr`.
+ *   - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call synchronises the host
+ *     and no call allocates or frees device memory -- the caller owns every buffer, scratch included.
+ *   - Return value: 0 on success, a negative FSB_E* code for an argument error detected on the host, or
+ *     FSB_CUDA_ERROR_BASE + cudaError_t when a launch failed.
+ *   - Inputs are assumed validated (indptr non-decreasing, indptr[0]==0, indptr[n_rows]==nnz,
+ *     0 <= indices < n_cols).  fsb_csr_analyze gathers what the host needs to check that in one pass.
+ *   - n_rows and n_cols must be < 2^31; nnz may exceed 2^31 when ptype is FSB_I64.
+ */
+#ifndef FSB_H_
+#define FSB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FSB_VERSION 100
+
+/* dtype tags */
+#define FSB_F32 0
+#define FSB_F64 1
+#define FSB_I32 0
+#define FSB_I64 1
+
+/* error codes (negative) */
+#define FSB_OK 0
+#define FSB_EINVAL (-1)      /* bad enum / negative size / null pointer where one is required */
+#define FSB_ERANGE (-2)      /* n_rows, n_cols or a tile count outside the supported range   */
+#define FSB_EALIGN (-3)      /* pointer not aligned to its element size                      */
+#define FSB_ESCRATCH (-4)    /* scratch buffer smaller than fsb_*_scratch_bytes() asks for   */
+#define FSB_CUDA_ERROR_BASE 1000
+
+/* SpMV algorithm selector */
+#define FSB_SPMV_AUTO 0
+#define FSB_SPMV_VECTOR 1    /* a group of 2..32 lanes per row; one launch, no scratch       */
+#define FSB_SPMV_STREAM 2    /* fixed-size nnz tiles (load-balanced); needs plan + scratch   */
+
+/* SpMM staging selector */
+#define FSB_SPMM_AUTO 0
+#define FSB_SPMM_PLAIN 1     /* tile of data/indices staged in shared memory by ordinary loads   */
+#define FSB_SPMM_BULK 2      /* tile staged by cp.async.bulk (TMA 1-D bulk copy) + mbarrier       */
+
+int fsb_version(void);
+
+/* nnz per tile of the tiled kernels (a power of two).  `tuning` is the value later passed to
+ * fsb_spmv_csr: bits 8-9 pick the SpMV tile (0 = default 2048, 1 = 1024, 3 = 4096). */
+int fsb_spmv_tile_nnz(int vtype, int tuning);
+int fsb_spmm_tile_nnz(int vtype);
+
+/*
+ * Statistics of a CSR structure, written to 8 consecutive int64 on the DEVICE (`stats`):
+ *   [0] indptr[0]            [1] indptr[n_rows]      [2] number of i with indptr[i+1] < indptr[i]
+ *   [3] min(indices)         [4] max(indices)        [5] max row length
+ *   [6] number of empty rows [7] number of rows longer than 32x the mean row length (rounded up)
+ * ([3] = INT64_MAX and [4] = INT64_MIN when nnz == 0; [5] = 0 when n_rows == 0.)
+ * Replaces the six separate device reductions + host syncs of the reference's
+ * _prepare_spmv_csr_matrix (src/flagsparse/sparse_operations/spmv_csr.py:404-427) and
+ * _prepare_spmm_csr_matrix (src/flagsparse/sparse_operations/spmm_csr.py:226-254): the host reads the
+ * eight numbers back with one copy.  `indices` may be NULL when nnz == 0.
+ */
+int fsb_csr_analyze(int itype, int ptype, const void* indices, const void* indptr, int64_t n_rows,
+                    int64_t nnz, int64_t* stats, void* stream);
+
+/*
+ * Tile plan: tile_row[t] for t = 0..n_tiles, n_tiles = ceil(nnz / tile_nnz), int32 on the device.
+ *   tile_row[0] = 0, tile_row[n_tiles] = n_rows, otherwise the row that holds nnz number t*tile_nnz.
+ * Rows [tile_row[t], tile_row[t+1]) are the rows whose last nnz lies in tile t (empty rows go to the
+ * tile in which their indptr value falls), i.e. the rows tile t writes.  Plays the part of the
+ * reference's row buckets (_build_spmv_opt_buckets, spmv_csr.py:281-327; _build_spmm_opt_buckets and
+ * _build_spmm_opt_split_metadata, spmm_csr.py:417-477): it is built once per matrix at prepare time.
+ */
+int64_t fsb_csr_num_tiles(int64_t nnz, int tile_nnz);
+int fsb_csr_tile_plan(int ptype, const void* indptr, int64_t n_rows, int64_t nnz, int tile_nnz,
+                      int32_t* tile_row, void* stream);
+
+/*
+ * y = A x for CSR A.  Replaces the launches in _triton_spmv_csr_impl_opt_prepared
+ * (spmv_csr.py:329-376, kernels :161-279) and _triton_spmv_csr_impl_prepared (:510-554, kernel :94-120).
+ * Every y[i] is written exactly once per call (empty rows get an exact 0), nothing else is written.
+ *   algo      FSB_SPMV_VECTOR needs neither tile_row nor scratch.
+ *             FSB_SPMV_STREAM needs tile_row from fsb_csr_tile_plan(tile_nnz = fsb_spmv_tile_nnz(vtype, tuning))
+ *             and `scratch` of at least fsb_spmv_csr_scratch_bytes() bytes, 16-byte aligned.
+ *             FSB_SPMV_AUTO picks STREAM when tile_row and scratch are given and nnz is large, else VECTOR.
+ *   tuning    0 = default; otherwise kernel-specific knob (VECTOR: lanes per row, a power of two 2..32;
+ *             STREAM: bits 0-7 = 1 + the right-shift applied to a tile's mean row length to get the
+ *             lanes per row; bits 8-9 = tile size, see fsb_spmv_tile_nnz).  Results stay within tolerance for any value; only speed changes.
+ * The result is deterministic: the same inputs give the same bits on every call (no floating atomics).
+ */
+size_t fsb_spmv_csr_scratch_bytes(int vtype, int64_t nnz, int tuning);
+int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, const void* indices,
+                 const void* indptr, const void* x, void* y, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                 int algo, int tuning, const int32_t* tile_row, void* scratch, size_t scratch_bytes,
+                 void* stream);
+
+/*
+ * Same product, but every finished y value is stored into n_peers output vectors (one per GPU of the
+ * box, the local one included) through peer-mapped pointers, at element offset row_offset + i: the
+ * SpMV epilogue doubles as the all-gather of the row-sharded driver.  y_peers is a DEVICE array of
+ * n_peers pointers.  Always uses the STREAM algorithm.  The reference has no multi-GPU path; this
+ * stands in for "each rank runs spmv_csr.py:329-376 on its row shard, then y is all-gathered".
+ */
+int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
+                         const void* indptr, const void* x, void* const* y_peers, int n_peers,
+                         int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int tuning,
+                         const int32_t* tile_row, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * C = A B for CSR A and dense row-major B (n_cols x n_dense, leading dimension ldb elements);
+ * C is n_rows x n_dense with leading dimension ldc.  Replaces _triton_spmm_csr_impl
+ * (spmm_csr.py:525-599, kernel :92-134) and _triton_spmm_csr_impl_opt_prepared (:1033-1055, kernels
+ * :602-919, split workspace :976-1030).  Every C[i, j] is written exactly once per call.
+ *   tile_row  from fsb_csr_tile_plan(tile_nnz = fsb_spmm_tile_nnz(vtype)).
+ *   scratch   at least fsb_spmm_csr_scratch_bytes() bytes, 16-byte aligned (per-tile partial rows of
+ *             rows that cross a tile boundary -- the counterpart of the reference's split workspace).
+ *   status    optional DEVICE int32; set to a non-zero code if a bounded wait on a bulk copy ran out
+ *             (the affected tiles are then left unwritten).  May be NULL.
+ */
+size_t fsb_spmm_csr_scratch_bytes(int vtype, int64_t nnz, int64_t n_dense);
+int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, const void* indices,
+                 const void* indptr, const void* B, int64_t ldb, void* C, int64_t ldc, int64_t n_rows,
+                 int64_t n_cols, int64_t n_dense, int64_t nnz, int algo, const int32_t* tile_row,
+                 void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FSB_H_ */

@@ -1,0 +1,187 @@
+"""Generate the golden fixtures of tests/golden/ by running the REFERENCE's own code on small seeded cases.
+
+Run from the repository root, in a container where the reference checkout is available:
+
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py --reference /path/to/flagsparse
+
+The reference's public entry points insist on CUDA tensors, so this script calls the functions right
+below them -- the same ones the entry points call -- on CPU tensors with Triton's interpreter executing
+the reference's @triton.jit kernels:
+  SpMV base path  _triton_spmv_csr_impl_prepared      (src/flagsparse/sparse_operations/spmv_csr.py:510-554)
+  SpMV opt path   _triton_spmv_csr_impl_opt_prepared  (:329-376) with _build_spmv_opt_buckets (:281-327)
+  SpMM base path  _triton_spmm_csr_impl               (src/flagsparse/sparse_operations/spmm_csr.py:525-599)
+  SpMM opt path   _run_spmm_opt_bucket / _run_spmm_opt_split_bucket (:922-1030), driven as in :1046-1055
+plus the pure host helpers (_resolve_spmm_alg1_launch_config, _select_spmm_opt_block_n,
+coo_to_csr_for_spmv).  Inputs and outputs are stored together, so the fixtures stay valid even if the
+synthetic generator changes.  Nothing here is imported by the package, the tests or the benchmark.
+"""
+
+import argparse
+import json
+import os
+import sys
+
+os.environ.setdefault("TRITON_INTERPRET", "1")
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from flagsparse_b200 import synthetic as S  # noqa: E402
+
+
+def _t(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def handmade_csr(seed, row_lens, n_cols, value_dtype, index_dtype, indptr_dtype):
+    rng = np.random.default_rng(seed)
+    indptr = np.zeros(len(row_lens) + 1, dtype=np.int64)
+    indptr[1:] = np.cumsum(row_lens)
+    cols = np.concatenate([np.sort(rng.choice(n_cols, size=k, replace=False)) for k in row_lens] or [np.zeros(0)])
+    data = rng.uniform(-1, 1, size=int(indptr[-1])).astype(value_dtype)
+    return data, cols.astype(index_dtype), indptr.astype(indptr_dtype)
+
+
+def spmv_cases():
+    out = {}
+    c1 = S.config_spec("c1").scaled(256)
+    out["c1_small"] = (S.generate_csr(c1), (256, 256), S.dense_vector(c1, 256))
+    c2 = S.config_spec("c2").scaled(512)
+    out["c2_small_f32"] = (S.generate_csr(c2), (512, 512), S.dense_vector(c2, 512))
+    out["c2_small_f64_i64"] = (
+        S.generate_csr(c2, value_dtype="float64", index_dtype="int64", indptr_dtype="int64"),
+        (512, 512), S.dense_vector(c2, 512, value_dtype="float64"))
+    c3 = S.config_spec("c3").scaled(2048)
+    out["c3_small"] = (S.generate_csr(c3), (2048, 2048), S.dense_vector(c3, 2048))
+    lens = [0, 0, 3, 0, 1, 300, 0, 0, 64, 65, 0, 33, 32, 31, 1, 1, 0, 700, 0, 0, 2, 0]
+    out["empty_rows_f32"] = (handmade_csr(11, lens, 1024, np.float32, np.int32, np.int32), (len(lens), 1024),
+                             np.random.default_rng(12).uniform(-1, 1, 1024).astype(np.float32))
+    out["empty_rows_f64"] = (handmade_csr(13, lens, 1024, np.float64, np.int32, np.int64), (len(lens), 1024),
+                             np.random.default_rng(14).uniform(-1, 1, 1024).astype(np.float64))
+    return out
+
+
+def spmm_cases():
+    out = {}
+    c4 = S.config_spec("c4").scaled(192)
+    csr = S.generate_csr(c4)
+    for n in (5, 12, 32, 64, 128):
+        out[f"c4_small_n{n}"] = (csr, (192, 192), S.dense_vector(c4, 192, n_dense=n))
+    lens = [1536, 4, 0, 2500, 0, 40, 130, 600]
+    out["long_rows_n48"] = (handmade_csr(21, lens, 4096, np.float32, np.int32, np.int64), (len(lens), 4096),
+                            np.random.default_rng(22).uniform(-1, 1, (4096, 48)).astype(np.float32))
+    out["long_rows_f64_n8"] = (handmade_csr(23, lens, 4096, np.float64, np.int64, np.int64), (len(lens), 4096),
+                               np.random.default_rng(24).uniform(-1, 1, (4096, 8)).astype(np.float64))
+    return out
+
+
+def run_reference_spmv(R, data, indices, indptr, shape, x):
+    """Mirror of prepare_spmv_csr (spmv_csr.py:455-495) minus the is_cuda gate, then both launch helpers."""
+    data, indices, indptr, x = _t(data), _t(indices), _t(indptr), _t(x)
+    n_rows, n_cols = shape
+    nnz = data.numel()
+    kernel_indices = indices.to(torch.int32) if indices.dtype == torch.int64 else indices
+    kernel_indptr = indptr.to(torch.int32) if nnz <= 2**31 - 1 else indptr.to(torch.int64)
+    row_lengths = kernel_indptr[1:] - kernel_indptr[:-1]
+    max_row_nnz = int(row_lengths.max().item()) if n_rows > 0 else 0
+    block_nnz = 256
+    max_segments = max((max_row_nnz + block_nnz - 1) // block_nnz, 1)
+    buckets = R._build_spmv_opt_buckets(row_lengths, max_row_nnz=max_row_nnz, row_index_dtype=torch.int32,
+                                        max_segments=None, fp64=data.dtype == torch.float64)
+    prepared = R.PreparedCsrSpmv(data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape,
+                                 n_rows=n_rows, n_cols=n_cols, block_nnz=block_nnz, max_segments=max_segments,
+                                 max_row_nnz=max_row_nnz, opt_buckets=buckets)
+    y_base = R._triton_spmv_csr_impl_prepared(prepared, x)
+    y_opt = R._triton_spmv_csr_impl_opt_prepared(prepared, x)
+    meta = [{"n_rows": int(b["rows"].numel()), "block_size": b["block_size"], "max_segs": b["max_segs"],
+             "batch_rows": b["batch_rows"]} for b in buckets]
+    return y_base.numpy(), y_opt.numpy(), meta
+
+
+def run_reference_spmm(M, data, indices, indptr, shape, B):
+    data, indices, indptr, B = _t(data), _t(indices), _t(indptr), _t(B)
+    n_rows, n_cols = shape
+    n_dense = int(B.shape[1])
+    kernel_indices = indices.to(torch.int32) if indices.dtype == torch.int64 else indices
+    kernel_indptr = indptr.to(torch.int64)
+    row_lengths = kernel_indptr[1:] - kernel_indptr[:-1]
+    max_row_nnz = int(row_lengths.max().item())
+    launch = M._resolve_spmm_alg1_launch_config(n_dense, max_row_nnz)
+    C_base = M._triton_spmm_csr_impl(data, kernel_indices, kernel_indptr, B, n_rows, n_dense,
+                                     block_n=launch["block_n"], block_nnz=launch["block_nnz"])
+    # opt path, as prepare_spmm_csr_opt (:480-522) + _triton_spmm_csr_impl_opt_prepared (:1046-1055)
+    buckets, long_rows = M._build_spmm_opt_buckets(row_lengths)
+    parts = (torch.empty((0,), dtype=long_rows.dtype), torch.empty((0,), dtype=torch.int64),
+             torch.empty((0,), dtype=torch.int64), torch.zeros(1, dtype=torch.int64))
+    if long_rows.numel() > 0:
+        parts = M._build_spmm_opt_split_metadata(kernel_indptr, long_rows, part_block_nnz=256)
+    prepared = M.PreparedCsrSpmmOpt(data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape,
+                                    n_rows=n_rows, n_cols=n_cols, row_lengths=row_lengths, max_row_nnz=max_row_nnz,
+                                    row_buckets=buckets, long_part_rows=parts[0], long_part_starts=parts[1],
+                                    long_part_ends=parts[2], long_row_ids=long_rows, long_row_part_ptr=parts[3],
+                                    long_row_fallback_only=False)
+    block_n = M._select_spmm_opt_block_n(n_dense)
+    C_opt = torch.zeros((n_rows, n_dense), dtype=B.dtype)
+    for bucket in buckets:
+        if bucket["kind"] == "split":
+            M._run_spmm_opt_split_bucket(prepared, B, C_opt, block_n)
+        else:
+            M._run_spmm_opt_bucket(prepared, bucket, B, C_opt, block_n)
+    meta = [{"kind": b["kind"], "n_rows": int(b["rows"].numel())} for b in buckets]
+    return C_base.numpy(), C_opt.numpy(), meta
+
+
+def host_helper_goldens(R, M):
+    g = {"alg1": [], "opt_block_n": {}, "coo": {}}
+    for n in (1, 4, 5, 8, 9, 16, 17, 24, 32, 33, 48, 64, 65, 96, 128, 256):
+        g["opt_block_n"][str(n)] = M._select_spmm_opt_block_n(n)
+        for max_row in (0, 1, 31, 32, 33, 1536, 5000):
+            for kw in ({}, {"block_nnz": 128}, {"block_n": 16, "block_nnz": 8}, {"block_nnz": 128, "max_segments": 4},
+                       {"max_segments": 1}, {"block_n": 0}, {"max_segments": 0}):
+                try:
+                    res = M._resolve_spmm_alg1_launch_config(n, max_row, **kw)
+                except Exception as exc:  # the exception TYPE is the contract
+                    res = {"raises": type(exc).__name__}
+                g["alg1"].append({"n": n, "max_row_nnz": max_row, "kw": kw, "result": res})
+    rng = np.random.default_rng(5)
+    row = rng.integers(0, 9, 40)
+    col = rng.integers(0, 7, 40)
+    val = rng.uniform(-1, 1, 40).astype(np.float32)
+    d, i, p = R.coo_to_csr_for_spmv(_t(val), _t(row), _t(col), (9, 7))
+    g["coo"] = {"row": row.tolist(), "col": col.tolist(), "val": val.tolist(), "data": d.tolist(),
+                "indices": i.tolist(), "indptr": p.tolist(), "indices_dtype": str(i.dtype), "indptr_dtype": str(p.dtype)}
+    return g
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, os.path.join(args.reference, "src"))
+    from flagsparse.sparse_operations import spmm_csr as M  # noqa: E402
+    from flagsparse.sparse_operations import spmv_csr as R  # noqa: E402
+
+    index = {"spmv": {}, "spmm": {}}
+    for name, ((data, indices, indptr), shape, x) in spmv_cases().items():
+        y_base, y_opt, meta = run_reference_spmv(R, data, indices, indptr, shape, x)
+        np.savez_compressed(os.path.join(HERE, f"spmv_{name}.npz"), data=data, indices=indices, indptr=indptr,
+                            shape=np.asarray(shape), x=x, y_base=y_base, y_opt=y_opt)
+        index["spmv"][name] = {"nnz": int(data.size), "buckets": meta}
+        print("spmv", name, data.size, meta, flush=True)
+    for name, ((data, indices, indptr), shape, B) in spmm_cases().items():
+        C_base, C_opt, meta = run_reference_spmm(M, data, indices, indptr, shape, B)
+        np.savez_compressed(os.path.join(HERE, f"spmm_{name}.npz"), data=data, indices=indices, indptr=indptr,
+                            shape=np.asarray(shape), B=B, C_base=C_base, C_opt=C_opt)
+        index["spmm"][name] = {"nnz": int(data.size), "buckets": meta}
+        print("spmm", name, data.size, meta, flush=True)
+    index["host"] = host_helper_goldens(R, M)
+    with open(os.path.join(HERE, "index.json"), "w") as f:
+        json.dump(index, f, indent=1, sort_keys=True)
+
+
+if __name__ == "__main__":
+    main()
