@@ -33,7 +33,7 @@ sys.path.insert(0, ROOT)
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures
 # summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"c2": 1.113e9}  # profiles/spmv_stream_c2_f32.md
 
 SPMV_WORKLOADS = {
     "c1": ("c1", "float32", "int32", "int32"),
