@@ -22,6 +22,7 @@ _ERRORS = {
     -2: "FSB_ERANGE (dimension outside the supported range)",
     -3: "FSB_EALIGN (pointer not aligned to its element size)",
     -4: "FSB_ESCRATCH (scratch buffer too small)",
+    -5: "FSB_ENOSPACE (matrix too large for the built-in scratch array)",
 }
 
 _c = ctypes
@@ -41,6 +42,7 @@ SIGNATURES = {
         _i32,
         [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp],
     ),
+    "fsb_spmv_csr_noalloc": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
     "fsb_spmm_csr_scratch_bytes": (_sz, [_i32, _i64, _i64]),
     "fsb_spmm_csr": (
         _i32,

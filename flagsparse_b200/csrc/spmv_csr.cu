@@ -15,6 +15,8 @@
 // in head[t] instead of y.  A second tiny kernel (one thread per tile) adds head[t] and the carries of
 // the tiles the row crossed, in a fixed order, and writes y -- no floating-point atomics anywhere, so
 // the result is bit-reproducible.
+#include <mutex>
+
 #include "fsb_common.cuh"
 
 namespace fsb {
@@ -439,5 +441,66 @@ extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void*
   if (!aligned_to(scratch, 16)) return FSB_EALIGN;
   SpmvArgs a{data, indices, indptr, x, nullptr, y_peers, n_peers, row_offset, n_rows, nnz,
              FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
+  return spmv_dispatch(vtype, itype, ptype, a);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the stream SpMV.
+//
+// Some hosts of this library may not create device memory at the moment they need a product: code running
+// while a memory pool is frozen or under a fixed-footprint policy, plugins that are handed tensors by a
+// framework but have no allocator of their own, and callers bound to a real-time loop where a cudaMalloc
+// (which can synchronise the whole device) is off limits.  For them the per-tile partial sums live in the
+// array below, which is part of the library image: it exists on every GPU that loads libfsb.so, from load
+// until the process exits, and is never resized.
+// ---------------------------------------------------------------------------------------------------
+namespace fsb {
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[(size_t)FSB_NOALLOC_MAX_TILES * 2 * sizeof(double)];
+
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_ptr[kMaxDevices];  // device address of the array above, per device ordinal
+static std::mutex g_noalloc_mutex;
+
+// The array's name is only a stand-in on the host; the address the kernels need comes from the runtime,
+// once per device, with that device current.
+static int noalloc_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (dev < 0 || dev >= kMaxDevices) return FSB_ERANGE;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_rc(e);
+    if (p == nullptr) return FSB_EINVAL;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return FSB_OK;
+}
+
+}  // namespace fsb
+
+extern "C" int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, const void* indices,
+                                    const void* indptr, const void* x, void* y, int64_t n_rows, int64_t n_cols,
+                                    int64_t nnz, int tuning, const int32_t* tile_row, void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
+  if (rc != FSB_OK) return rc;
+  if (n_rows == 0) return FSB_OK;
+  if (y == nullptr) return FSB_EINVAL;
+  const size_t sv = vtype == FSB_F32 ? 4 : 8;
+  if (!aligned_to(y, sv)) return FSB_EALIGN;
+  if (nnz == 0) return cuda_rc(cudaMemsetAsync(y, 0, (size_t)n_rows * sv, st));
+  if (tile_row == nullptr) return FSB_EINVAL;
+  // the built-in array holds two partial sums per tile for at most FSB_NOALLOC_MAX_TILES tiles
+  const int64_t n_tiles = fsb_csr_num_tiles(nnz, fsb_spmv_tile_nnz(vtype, tuning));
+  if (n_tiles > FSB_NOALLOC_MAX_TILES) return FSB_ENOSPACE;
+  void* scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);
+  if (rc != FSB_OK) return rc;
+  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, n_rows, nnz, FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
   return spmv_dispatch(vtype, itype, ptype, a);
 }

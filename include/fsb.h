@@ -42,6 +42,7 @@ extern "C" {
 #define FSB_ERANGE (-2)      /* n_rows, n_cols or a tile count outside the supported range   */
 #define FSB_EALIGN (-3)      /* pointer not aligned to its element size                      */
 #define FSB_ESCRATCH (-4)    /* scratch buffer smaller than fsb_*_scratch_bytes() asks for   */
+#define FSB_ENOSPACE (-5)    /* problem too large for the library's built-in scratch array   */
 #define FSB_CUDA_ERROR_BASE 1000
 
 /* SpMV algorithm selector */
@@ -117,6 +118,30 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
                          const void* indptr, const void* x, void* const* y_peers, int n_peers,
                          int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int tuning,
                          const int32_t* tile_row, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * y = A x with the STREAM algorithm for callers that must not (or cannot) allocate device memory: code
+ * running inside a frozen or fixed-size memory pool, plugins that only ever receive buffers from their
+ * host framework, latency-critical loops where cudaMalloc's device-wide synchronisation is unacceptable.
+ * This entry point has no counterpart in the reference (its Triton launches allocate through torch).
+ * The per-tile partial sums that fsb_spmv_csr keeps in caller scratch live here in an array that is part
+ * of the library image -- FSB_NOALLOC_MAX_TILES tiles, 4 MiB, resident on every GPU that loads the
+ * library until the process exits.  The call itself allocates and frees nothing; inputs, y and tile_row
+ * (fsb_csr_tile_plan with tile_nnz = fsb_spmv_tile_nnz(vtype, tuning)) still come from the caller.
+ *   - Limit: ceil(nnz / tile_nnz) <= FSB_NOALLOC_MAX_TILES (about 5.3e8 nnz at the default tile of 2048);
+ *     a larger matrix is refused with FSB_ENOSPACE before anything is launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the previous call left in it.
+ *     Nothing in it needs clearing -- each launch writes every slot it later reads -- but two calls that
+ *     overlap on the GPU (different streams, or different host threads) would overwrite each other's
+ *     partial sums: serialise them.
+ * Results are bit-identical to fsb_spmv_csr(FSB_SPMV_STREAM) with the same tuning.
+ */
+#define FSB_NOALLOC_MAX_TILES 262144
+int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, const void* indices,
+                         const void* indptr, const void* x, void* y, int64_t n_rows, int64_t n_cols,
+                         int64_t nnz, int tuning, const int32_t* tile_row, void* stream);
 
 /*
  * C = A B for CSR A and dense row-major B (n_cols x n_dense, leading dimension ldb elements);
