@@ -345,7 +345,7 @@ def run_ours(args, workload):
             op = fs.ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=args.exchange)
             step = lambda: op.matvec(x)  # noqa: E731
             launches_per_step = 2  # tile kernel + fix-up (the barrier / NCCL kernels are not ours)
-            si, sp_ = 4, 8
+            si, sp_ = op.prepared.kernel_indices.element_size(), op.prepared.kernel_indptr.element_size()
             extra["exchange"] = op.mode
             extra["shard_nnz"] = d.numel()
             my_rows = (r0, r1)

@@ -42,14 +42,19 @@ struct PeerOut {
 };
 
 // ---------------------------------------------------------------------------------------------------
-// vector kernel: L lanes per row, scalar coalesced loads, two accumulators per lane
+// vector kernel: L lanes per row.
+//   ALIGNED: every lane reads whole 4-element groups of `data` / `indices` (one or two 128-bit loads
+//            each) starting at the group that contains the row's first entry; entries of neighbouring rows
+//            that share the first or last group are masked off.  A row of 32 entries then costs two or three
+//            requests per array instead of one per eight entries.
+//   otherwise: scalar loads, used when the arrays are not 16-byte aligned.
 // ---------------------------------------------------------------------------------------------------
-template <typename V, typename I, typename P, int L>
+template <typename V, typename I, typename P, int L, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) spmv_vector_kernel(const V* __restrict__ data,
                                                               const I* __restrict__ idx,
                                                               const P* __restrict__ ptr,
                                                               const V* __restrict__ x, V* __restrict__ y,
-                                                              int64_t n_rows) {
+                                                              int64_t n_rows, int64_t nnz) {
   const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   const int64_t row = gtid / L;
   const int lane = (int)(gtid % L);
@@ -59,14 +64,40 @@ __global__ void __launch_bounds__(kThreads) spmv_vector_kernel(const V* __restri
     e = (int64_t)ptr[row + 1];
   }
   V acc0 = 0, acc1 = 0;
-  int64_t p = s + lane;
-  for (; p + L < e; p += 2 * L) {
-    const V a0 = ld_stream(data + p), a1 = ld_stream(data + p + L);
-    const int64_t c0 = (int64_t)ld_stream(idx + p), c1 = (int64_t)ld_stream(idx + p + L);
-    acc0 += a0 * __ldg(x + c0);
-    acc1 += a1 * __ldg(x + c1);
+  if (ALIGNED) {
+    const int64_t full = nnz & ~(int64_t)3;  // groups below this index lie wholly inside the arrays
+    for (int64_t q = (s & ~(int64_t)3) + 4 * lane; q < e; q += 4 * L) {
+      V a[4];
+      I c[4];
+      if (q + 4 <= full) {
+        ld_stream4(data + q, a);
+        ld_stream4(idx + q, c);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          a[j] = (q + j < nnz) ? data[q + j] : (V)0;
+          c[j] = (q + j < nnz) ? idx[q + j] : (I)0;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int64_t pp = q + j;
+        if (pp >= s && pp < e) {
+          if (j & 1) acc1 += a[j] * __ldg(x + (int64_t)c[j]);
+          else acc0 += a[j] * __ldg(x + (int64_t)c[j]);
+        }
+      }
+    }
+  } else {
+    int64_t p = s + lane;
+    for (; p + L < e; p += 2 * L) {
+      const V a0 = ld_stream(data + p), a1 = ld_stream(data + p + L);
+      const int64_t c0 = (int64_t)ld_stream(idx + p), c1 = (int64_t)ld_stream(idx + p + L);
+      acc0 += a0 * __ldg(x + c0);
+      acc1 += a1 * __ldg(x + c1);
+    }
+    if (p < e) acc0 += ld_stream(data + p) * __ldg(x + (int64_t)ld_stream(idx + p));
   }
-  if (p < e) acc0 += ld_stream(data + p) * __ldg(x + (int64_t)ld_stream(idx + p));
   V acc = acc0 + acc1;
 #pragma unroll
   for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
@@ -250,11 +281,15 @@ static int ipt_of(int tuning) {
 
 template <typename V, typename I, typename P, int L>
 static void launch_vector(const void* data, const void* idx, const void* ptr, const void* x, void* y,
-                          int64_t n_rows, cudaStream_t st) {
+                          int64_t n_rows, int64_t nnz, cudaStream_t st) {
   const int64_t threads = n_rows * L;
-  const int64_t g = (threads + kThreads - 1) / kThreads;
-  spmv_vector_kernel<V, I, P, L><<<(unsigned)g, kThreads, 0, st>>>((const V*)data, (const I*)idx,
-                                                                   (const P*)ptr, (const V*)x, (V*)y, n_rows);
+  const unsigned g = (unsigned)((threads + kThreads - 1) / kThreads);
+  if (aligned_to(data, 16) && aligned_to(idx, 16))
+    spmv_vector_kernel<V, I, P, L, true><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
+                                                                 (const V*)x, (V*)y, n_rows, nnz);
+  else
+    spmv_vector_kernel<V, I, P, L, false><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
+                                                                  (const V*)x, (V*)y, n_rows, nnz);
 }
 
 template <typename V, typename I, typename P>
@@ -262,17 +297,18 @@ static int run_vector(const void* data, const void* idx, const void* ptr, const 
                       int64_t n_rows, int64_t nnz, int tuning, cudaStream_t st) {
   int L = tuning & 0xff;
   if (L == 0) {
+    // about eight entries (two 4-element groups) per lane
     const int64_t mean = n_rows > 0 ? nnz / n_rows : 0;
     L = 2;
-    while (L < 32 && 2 * L <= mean) L <<= 1;  // about two elements per lane
+    while (L < 32 && 8 * L < mean + 3) L <<= 1;
   }
   if (n_rows * (int64_t)L / kThreads >= INT32_MAX) return FSB_ERANGE;
   switch (L) {
-    case 2: launch_vector<V, I, P, 2>(data, idx, ptr, x, y, n_rows, st); break;
-    case 4: launch_vector<V, I, P, 4>(data, idx, ptr, x, y, n_rows, st); break;
-    case 8: launch_vector<V, I, P, 8>(data, idx, ptr, x, y, n_rows, st); break;
-    case 16: launch_vector<V, I, P, 16>(data, idx, ptr, x, y, n_rows, st); break;
-    case 32: launch_vector<V, I, P, 32>(data, idx, ptr, x, y, n_rows, st); break;
+    case 2: launch_vector<V, I, P, 2>(data, idx, ptr, x, y, n_rows, nnz, st); break;
+    case 4: launch_vector<V, I, P, 4>(data, idx, ptr, x, y, n_rows, nnz, st); break;
+    case 8: launch_vector<V, I, P, 8>(data, idx, ptr, x, y, n_rows, nnz, st); break;
+    case 16: launch_vector<V, I, P, 16>(data, idx, ptr, x, y, n_rows, nnz, st); break;
+    case 32: launch_vector<V, I, P, 32>(data, idx, ptr, x, y, n_rows, nnz, st); break;
     default: return FSB_EINVAL;
   }
   FSB_RETURN_IF_LAUNCH_FAILED();

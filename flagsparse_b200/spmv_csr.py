@@ -29,6 +29,9 @@ from ._common import (
 _STREAM_MIN_NNZ = 1 << 18
 # the vector kernel gives a row to at most 32 lanes, so it is kept away from very long rows
 _VECTOR_MAX_ROW_NNZ = 4096
+# "uniform" rows: the longest row is within this factor (plus a small allowance) of the mean row length
+_UNIFORM_ROW_FACTOR = 8
+_UNIFORM_ROW_SLACK = 64
 
 _ALGO_NAMES = {"auto": _lib.FSB_SPMV_AUTO, "vector": _lib.FSB_SPMV_VECTOR, "stream": _lib.FSB_SPMV_STREAM}
 
@@ -48,12 +51,19 @@ def _resolve_block_nnz(max_row_nnz, block_nnz, max_segments):
 
 
 def _select_spmv_algo(n_rows, nnz, max_row_nnz):
-    """Kernel choice from indptr statistics: the nnz-tiled stream kernel whenever the matrix is big
-    enough to fill the GPU or has long rows, else the lanes-per-row vector kernel."""
+    """Kernel choice from indptr statistics.  Rows of about equal length (longest row within a small
+    factor of the mean) go to the lanes-per-row vector kernel, which needs one launch, no scratch, and leaves
+    the whole L1 to the gathers of x; skewed row lengths go to the nnz-tiled stream kernel, whose work per
+    CTA does not depend on the row structure.  Small matrices take the vector kernel unless a row is long."""
     forced = os.environ.get("FSB_SPMV_ALGO", "").strip().lower()
     if forced in ("vector", "stream"):
         return _ALGO_NAMES[forced]
-    if nnz < _STREAM_MIN_NNZ and max_row_nnz <= _VECTOR_MAX_ROW_NNZ:
+    if max_row_nnz > _VECTOR_MAX_ROW_NNZ:
+        return _lib.FSB_SPMV_STREAM
+    if nnz < _STREAM_MIN_NNZ:
+        return _lib.FSB_SPMV_VECTOR
+    mean = nnz / max(n_rows, 1)
+    if max_row_nnz <= _UNIFORM_ROW_FACTOR * mean + _UNIFORM_ROW_SLACK:
         return _lib.FSB_SPMV_VECTOR
     return _lib.FSB_SPMV_STREAM
 

@@ -165,10 +165,12 @@ def test_coo_to_csr_matches_reference():
 def test_algo_selector():
     sel = spmv_csr._select_spmv_algo
     assert sel(4096, 65536, 16) == _lib.FSB_SPMV_VECTOR
-    assert sel(1 << 22, 1 << 27, 70) == _lib.FSB_SPMV_STREAM
+    assert sel(1 << 22, 1 << 27, 70) == _lib.FSB_SPMV_VECTOR      # Poisson(32): uniform rows
+    assert sel(1 << 24, 248_000_000, 1 << 17) == _lib.FSB_SPMV_STREAM  # power-law rows
+    assert sel(1 << 22, 1 << 24, 2000) == _lib.FSB_SPMV_STREAM    # mean 4, a few rows of 2000
     assert sel(10, 50000, 40000) == _lib.FSB_SPMV_STREAM  # long rows go to the tiled kernel even when small
-    os.environ["FSB_SPMV_ALGO"] = "vector"
+    os.environ["FSB_SPMV_ALGO"] = "stream"
     try:
-        assert sel(1 << 22, 1 << 27, 70) == _lib.FSB_SPMV_VECTOR
+        assert sel(1 << 22, 1 << 27, 70) == _lib.FSB_SPMV_STREAM
     finally:
         del os.environ["FSB_SPMV_ALGO"]

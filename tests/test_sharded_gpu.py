@@ -51,8 +51,11 @@ def _worker(rank, world, port, result_dir):
                 y = op.matvec(x * float(rep + 1))
             torch.cuda.synchronize()
             results[mode] = y.clone()
-        assert torch.equal(results["nccl"], results["peer"])
+        # the two modes may run different kernels (different order of additions): each is held to the
+        # oracle bound by the parent; here only that they agree closely
+        assert torch.allclose(results["nccl"], results["peer"], rtol=1e-4, atol=1e-4)
         np.save(os.path.join(result_dir, f"y{rank}.npy"), results["peer"].cpu().numpy())
+        np.save(os.path.join(result_dir, f"n{rank}.npy"), results["nccl"].cpu().numpy())
     finally:
         dist.destroy_process_group()
 
@@ -67,8 +70,11 @@ def test_two_ranks_nccl_and_peer(cuda, fsb_lib, tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     y0, y1 = np.load(tmp_path / "y0.npy"), np.load(tmp_path / "y1.npy")
-    assert np.array_equal(y0, y1)
+    assert np.array_equal(y0, y1)  # every rank holds the same assembled vector
+    n0, n1 = np.load(tmp_path / "n0.npy"), np.load(tmp_path / "n1.npy")
+    assert np.array_equal(n0, n1)
     spec = S.config_spec("c5").scaled(1 << 18)
     d, i, p = S.generate_csr(spec, None, indptr_dtype="int64")
     x = S.dense_vector(spec, spec.n_cols) * np.float32(3.0)
-    assert_spmv_ok(y0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks")
+    assert_spmv_ok(y0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores")
+    assert_spmv_ok(n0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, nccl")

@@ -168,6 +168,14 @@ def test_c_abi_direct_call_with_unaligned_arrays(cuda, fsb_lib):
                               plan.data_ptr(), scratch.data_ptr(), nbytes, st)
     assert rc == 0
     assert_spmv_ok(y.cpu().numpy(), data, idx, ptr, (spec.n_rows, spec.n_cols), x, what="unaligned")
+    # the vector kernel on the same unaligned arrays (scalar loads) and on aligned ones (128-bit groups)
+    for dd, ii in ((d1, i1), (dev(data), dev(idx))):
+        y.fill_(float("nan"))
+        rc = fsb_lib.fsb_spmv_csr(_lib.FSB_F32, _lib.FSB_I32, _lib.FSB_I32, dd.data_ptr(), ii.data_ptr(), p.data_ptr(),
+                                  xd.data_ptr(), y.data_ptr(), spec.n_rows, spec.n_cols, nnz, _lib.FSB_SPMV_VECTOR, 0,
+                                  None, None, 0, st)
+        assert rc == 0
+        assert_spmv_ok(y.cpu().numpy(), data, idx, ptr, (spec.n_rows, spec.n_cols), x, what="vector direct")
     # too little scratch and a misaligned value pointer are refused, not launched
     assert fsb_lib.fsb_spmv_csr(_lib.FSB_F32, _lib.FSB_I32, _lib.FSB_I32, d1.data_ptr(), i1.data_ptr(), p.data_ptr(),
                                 xd.data_ptr(), y.data_ptr(), spec.n_rows, spec.n_cols, nnz, _lib.FSB_SPMV_STREAM, 0,
@@ -224,9 +232,12 @@ def test_config_c2_full_size(cuda, fsb_lib, vdt, idt):
     d, i, p = S.generate_csr(spec, "cuda:0", value_dtype=vdt, index_dtype=idt, indptr_dtype=idt)
     x = S.dense_vector(spec, spec.n_cols, "cuda:0", value_dtype=vdt)
     prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
-    assert prep.algo == _lib.FSB_SPMV_STREAM
+    assert prep.algo == _lib.FSB_SPMV_VECTOR  # uniform row lengths
     y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
     worst = check_spmv_blocks(spec, y, x.cpu().numpy(), sample_blocks(spec.n_rows, 24, 2048), vdt, idt, idt)
+    with env(FSB_SPMV_ALGO="stream"):
+        ys = fs.flagsparse_spmv_csr(d, i, p, x, (spec.n_rows, spec.n_cols))
+    check_spmv_blocks(spec, ys, x.cpu().numpy(), sample_blocks(spec.n_rows, 8, 2048, seed=1), vdt, idt, idt)
     assert torch.equal(fs.flagsparse_spmv_csr(x=x * 2, prepared=prep), y * 2)
     assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)
     print(f"c2 {vdt}: nnz {d.numel()}, worst bound ratio {worst:.2e}")
