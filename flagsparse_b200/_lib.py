@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libfsb.so")
 FSB_F32, FSB_F64 = 0, 1
 FSB_I32, FSB_I64 = 0, 1
 FSB_SPMV_AUTO, FSB_SPMV_VECTOR, FSB_SPMV_STREAM = 0, 1, 2
+FSB_SPMV_PANEL = 3  # host-side tag only: the panel kernel has its own entry point
 FSB_SPMM_AUTO, FSB_SPMM_PLAIN, FSB_SPMM_BULK = 0, 1, 2
 FSB_CUDA_ERROR_BASE = 1000
 
@@ -43,6 +44,9 @@ SIGNATURES = {
         [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp],
     ),
     "fsb_spmv_csr_noalloc": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
+    "fsb_spmv_panel_piece_slots": (_i32, []),
+    "fsb_spmv_panel_smem_bytes": (_sz, [_i32, _i32, _i32]),
+    "fsb_spmv_csr_panel": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i64, _i64, _vp, _vp]),
     "fsb_spmm_csr_scratch_bytes": (_sz, [_i32, _i64, _i64]),
     "fsb_spmm_csr": (
         _i32,

@@ -16,6 +16,7 @@ inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? FSB_OK : FSB_CUDA_
   } while (0)
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+__device__ __forceinline__ bool aligned_to_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // ---- streaming (read-once) loads: evict-first so that A does not push x / B out of L2 -------------
 template <typename T>

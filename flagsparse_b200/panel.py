@@ -1,0 +1,180 @@
+"""Prepare-time regrouping of a CSR matrix for the panel SpMV kernel (csrc/spmv_panel.cu).
+
+The reference's prepare step builds row-length buckets (src/flagsparse/sparse_operations/spmv_csr.py:281-327);
+this one builds, for matrices whose rows reach a limited range of columns, a second copy of the entries
+grouped into units = (block of RB rows) x (chunk of CW columns), so that the kernel can keep the part of x a
+unit needs in shared memory.  It runs once per matrix, off the timed path, with torch operations on the
+device; the product itself is one launch of fsb_spmv_csr_panel.
+"""
+
+import torch
+
+from . import _lib
+from ._common import _VTYPE
+
+SM_COUNT_FALLBACK = 148
+CTAS_PER_SM = 2
+# the kernel is worth its second copy of the matrix only when the extra reads of x and the padding stay small
+MAX_X_OVERHEAD = 0.40       # bytes of x chunks loaded / bytes of entries streamed
+MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
+MAX_RUN = 32                # entries of one row inside one unit (they must fit one piece with room to spare)
+MAX_ROW_NNZ = 512
+MIN_NNZ = 1 << 22
+NO_ROW = 0xFFFF
+
+
+class PanelLayout:
+    """Device arrays of the regrouped matrix plus the launch geometry."""
+
+    __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "rb_unit_ptr", "n_row_blocks", "rb_rows", "chunk_cols",
+                 "n_units", "n_pieces", "x_overhead", "slot_overhead", "status")
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.val, self.rc, self.unit_piece_ptr, self.unit_chunk,
+                                                           self.rb_unit_ptr))
+
+
+def _geometry(dtype, n_rows, device):
+    L = _lib.lib()
+    vt = _VTYPE[dtype]
+    sv = 4 if dtype == torch.float32 else 8
+    chunk_cols = 4096 if sv == 4 else 2048
+    try:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+    except Exception:
+        sms = SM_COUNT_FALLBACK
+    budget = (222 * 1024) // CTAS_PER_SM - 1024      # shared memory per CTA, two CTAs per SM
+    fixed = int(L.fsb_spmv_panel_smem_bytes(vt, 0, chunk_cols))
+    rb_cap = min(32768, (budget - fixed) // sv // 64 * 64)
+    rb_rows = min(rb_cap, max(1024, -(-n_rows // (sms * CTAS_PER_SM))))  # one wave of CTAs when the matrix allows
+    rb_rows = -(-rb_rows // 4) * 4
+    return vt, sv, chunk_cols, rb_rows, int(L.fsb_spmv_panel_piece_slots())
+
+
+def estimate_units(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
+    """Number of non-empty (row block, column chunk) units, without sorting anything."""
+    n_rb = -(-n_rows // rb_rows)
+    n_ch = -(-n_cols // chunk_cols)
+    if n_rb * n_ch > (1 << 27):
+        return None
+    lens = (indptr[1:] - indptr[:-1]).to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(n_rows, device=indices.device), lens)
+    key = (rows // rb_rows) * n_ch + indices.to(torch.int64) // chunk_cols
+    mark = torch.zeros(n_rb * n_ch, dtype=torch.bool, device=indices.device)
+    mark[key] = True
+    return int(mark.sum().item())
+
+
+def _cumsum0(counts):
+    out = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
+    torch.cumsum(counts, 0, out=out[1:])
+    return out
+
+
+def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False):
+    """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
+    nnz = data.numel()
+    if nnz == 0 or n_rows == 0 or n_cols == 0 or nnz >= 2**31 - 64:
+        return None
+    if not force and (nnz < MIN_NNZ or max_row_nnz > MAX_ROW_NNZ):
+        return None
+    dev = data.device
+    vt, sv, CW, RB, SLOTS = _geometry(data.dtype, n_rows, dev)
+    n_rb = -(-n_rows // RB)
+    n_ch = -(-n_cols // CW)
+    if not force:
+        n_units = estimate_units(indices, indptr, n_rows, n_cols, RB, CW)
+        if n_units is None or n_units * CW * sv > MAX_X_OVERHEAD * nnz * (sv + 4):
+            return None
+    lens = (indptr[1:] - indptr[:-1]).to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(n_rows, device=dev), lens)
+    cols = indices.to(torch.int64)
+    key = (rows // RB) * n_ch + cols // CW
+    key_sorted, perm = torch.sort(key, stable=True)   # entries keep their row-major order inside a unit
+    del key
+    ukey, ucnt = torch.unique_consecutive(key_sorted, return_counts=True)
+    n_units = ukey.numel()
+    u_rb = ukey // n_ch
+    u_ch = ukey % n_ch
+    ustart = _cumsum0(ucnt)
+    unit_of_entry = torch.repeat_interleave(torch.arange(n_units, device=dev), ucnt)
+    rows_p = rows[perm]
+    cols_p = cols[perm]
+    del rows, cols, key_sorted
+    ar = torch.arange(nnz, device=dev)
+    j = ar - ustart[unit_of_entry]                     # position inside the unit
+    # runs: maximal groups of consecutive entries of one row inside one unit
+    new_run = torch.ones(nnz, dtype=torch.bool, device=dev)
+    new_run[1:] = (rows_p[1:] != rows_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
+    run_id = torch.cumsum(new_run.to(torch.int64), 0) - 1
+    n_runs = int(run_id[-1].item()) + 1
+    run_first = ar[new_run]                            # global index of each run's first entry
+    run_end = torch.empty(n_runs, dtype=torch.int64, device=dev)
+    run_end[:-1] = run_first[1:]
+    run_end[-1] = nnz
+    max_run = int((run_end - run_first).max().item())
+    del run_end
+    if max_run > MAX_RUN:
+        return None
+    # Pieces: greedy packing of whole runs into pieces of at most SLOTS entries, all units advancing one
+    # piece per step (the cut after a piece that starts at s is the last run boundary at or before s + SLOTS).
+    uend = ustart[1:]
+    cur = ustart[:-1].clone()
+    active = torch.arange(n_units, device=dev)
+    cuts = [cur.clone()]
+    while True:
+        t = cur[active] + SLOTS
+        end_a = uend[active]
+        inside = t < end_a
+        nxt = torch.where(inside, run_first[run_id[torch.clamp(t, max=nnz - 1)]], end_a)
+        cur[active] = nxt
+        keep = nxt < end_a
+        if not bool(keep.any()):
+            break
+        active = active[keep]
+        cuts.append(nxt[keep])
+    piece_start = torch.sort(torch.cat(cuts)).values          # global index of each piece's first entry
+    n_pieces = piece_start.numel()
+    if not force and n_pieces * SLOTS > MAX_SLOT_OVERHEAD * nnz + 4096:
+        return None
+    piece = torch.searchsorted(piece_start, ar, right=True) - 1
+    slot = ar - piece_start[piece]
+    pos = piece * SLOTS + slot
+    upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
+    del j, run_id, new_run, cuts, piece_start, slot
+    # ordinal of a unit inside its row block decides which of the two x buffers it uses
+    rb_unit_ptr = torch.searchsorted(u_rb.contiguous(), torch.arange(n_rb + 1, device=dev))
+    u_ord = torch.arange(n_units, device=dev) - rb_unit_ptr[u_rb]
+    rloc = rows_p - (rows_p // RB) * RB
+    field = (u_ord[unit_of_entry] & 1) * CW + (cols_p - (cols_p // CW) * CW)
+    del rows_p, cols_p
+    val = torch.zeros(n_pieces * SLOTS, dtype=data.dtype, device=dev)
+    val[pos] = data[perm]
+    word = (rloc << 16) | field                         # fits 32 bits: local row < 65535
+    word = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
+    rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)
+    rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
+    rc[pos] = word
+    del pos, perm, rloc, field, unit_of_entry, word
+
+    lay = PanelLayout()
+    lay.val, lay.rc = val, rc
+    lay.unit_piece_ptr = upiece.to(torch.int32)
+    lay.unit_chunk = u_ch.to(torch.int32)
+    lay.rb_unit_ptr = rb_unit_ptr.to(torch.int32)
+    lay.n_row_blocks, lay.rb_rows, lay.chunk_cols = n_rb, RB, CW
+    lay.n_units, lay.n_pieces = n_units, n_pieces
+    lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
+    lay.slot_overhead = n_pieces * SLOTS / float(nnz)
+    lay.status = torch.zeros(1, dtype=torch.int32, device=dev)
+    return lay
+
+
+def launch_panel(layout, x, y, n_rows, n_cols, stream_ptr):
+    L = _lib.lib()
+    rc = L.fsb_spmv_csr_panel(
+        _VTYPE[layout.val.dtype], layout.val.data_ptr(), layout.rc.data_ptr(), layout.unit_piece_ptr.data_ptr(),
+        layout.unit_chunk.data_ptr(), layout.rb_unit_ptr.data_ptr(), layout.n_row_blocks, layout.rb_rows,
+        layout.chunk_cols, x.data_ptr(), y.data_ptr(), n_rows, n_cols, layout.status.data_ptr(), stream_ptr,
+    )
+    _lib.check(rc, "fsb_spmv_csr_panel")

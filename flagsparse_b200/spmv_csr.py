@@ -32,8 +32,11 @@ _VECTOR_MAX_ROW_NNZ = 4096
 # "uniform" rows: the longest row is within this factor (plus a small allowance) of the mean row length
 _UNIFORM_ROW_FACTOR = 8
 _UNIFORM_ROW_SLACK = 64
+# regroup banded matrices for the panel kernel (costs a second copy of the entries); FSB_SPMV_PANEL=0 turns it off
+_PANEL_ENABLED = os.environ.get("FSB_SPMV_PANEL", "1") != "0"
 
-_ALGO_NAMES = {"auto": _lib.FSB_SPMV_AUTO, "vector": _lib.FSB_SPMV_VECTOR, "stream": _lib.FSB_SPMV_STREAM}
+_ALGO_NAMES = {"auto": _lib.FSB_SPMV_AUTO, "vector": _lib.FSB_SPMV_VECTOR, "stream": _lib.FSB_SPMV_STREAM,
+               "panel": _lib.FSB_SPMV_PANEL}
 
 
 def _resolve_block_nnz(max_row_nnz, block_nnz, max_segments):
@@ -56,7 +59,7 @@ def _select_spmv_algo(n_rows, nnz, max_row_nnz):
     the whole L1 to the gathers of x; skewed row lengths go to the nnz-tiled stream kernel, whose work per
     CTA does not depend on the row structure.  Small matrices take the vector kernel unless a row is long."""
     forced = os.environ.get("FSB_SPMV_ALGO", "").strip().lower()
-    if forced in ("vector", "stream"):
+    if forced in ("vector", "stream", "panel"):
         return _ALGO_NAMES[forced]
     if max_row_nnz > _VECTOR_MAX_ROW_NNZ:
         return _lib.FSB_SPMV_STREAM
@@ -79,11 +82,11 @@ class PreparedCsrSpmv:
     __slots__ = (
         "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "block_nnz",
         "max_segments", "max_row_nnz", "opt_buckets", "supports_opt", "stats", "algo", "tuning",
-        "tile_nnz", "tile_row", "scratch",
+        "tile_nnz", "tile_row", "scratch", "panel",
     )
 
     def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
-                 max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch):
+                 max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch, panel=None):
         self.data = data
         self.kernel_indices = kernel_indices
         self.kernel_indptr = kernel_indptr
@@ -100,11 +103,10 @@ class PreparedCsrSpmv:
         self.tile_nnz = tile_nnz
         self.tile_row = tile_row
         self.scratch = scratch
+        self.panel = panel
         n_tiles = 0 if tile_row is None else tile_row.numel() - 1
-        self.opt_buckets = [
-            {"kind": "stream" if algo == _lib.FSB_SPMV_STREAM else "vector", "tile_nnz": tile_nnz,
-             "n_tiles": n_tiles, "n_rows": n_rows}
-        ]
+        kind = {_lib.FSB_SPMV_STREAM: "stream", _lib.FSB_SPMV_PANEL: "panel"}.get(algo, "vector")
+        self.opt_buckets = [{"kind": kind, "tile_nnz": tile_nnz, "n_tiles": n_tiles, "n_rows": n_rows}]
 
 
 def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
@@ -179,7 +181,16 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     nnz = data.numel()
     algo = _select_spmv_algo(n_rows, nnz, max_row_nnz)
     tuning = int(os.environ.get("FSB_SPMV_TUNING", "0"))
-    tile_nnz, tile_row, scratch = 0, None, None
+    tile_nnz, tile_row, scratch, panel_layout = 0, None, None, None
+    # rows of about equal length whose columns stay within a few chunks: regroup once, keep x in shared memory
+    want_panel = algo == _lib.FSB_SPMV_PANEL or (
+        algo == _lib.FSB_SPMV_VECTOR and os.environ.get("FSB_SPMV_ALGO", "") == "" and _PANEL_ENABLED)
+    if want_panel:
+        from . import panel
+
+        panel_layout = panel.build_panel_layout(data, kernel_indices, kernel_indptr, n_rows, n_cols, max_row_nnz,
+                                                force=algo == _lib.FSB_SPMV_PANEL)
+        algo = _lib.FSB_SPMV_PANEL if panel_layout is not None else _lib.FSB_SPMV_VECTOR
     if algo == _lib.FSB_SPMV_STREAM and nnz > 0 and n_rows > 0:
         L = _lib.lib()
         vt = _VTYPE[data.dtype]
@@ -191,6 +202,7 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
         data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape, n_rows=n_rows,
         n_cols=n_cols, block_nnz=block_nnz_use, max_segments=max_segments_use, max_row_nnz=max_row_nnz,
         stats=stats, algo=algo, tuning=tuning, tile_nnz=tile_nnz, tile_row=tile_row, scratch=scratch,
+        panel=panel_layout,
     )
 
 
@@ -201,6 +213,12 @@ def _spmv_launch(prepared, x, y):
     L = _lib.lib()
     p = prepared
     dev = p.data.device
+    if p.algo == _lib.FSB_SPMV_PANEL and p.panel is not None:
+        from . import panel
+
+        with torch.cuda.device(dev):
+            panel.launch_panel(p.panel, x, y, p.n_rows, p.n_cols, _stream_ptr(dev))
+        return
     algo = p.algo if p.tile_row is not None else _lib.FSB_SPMV_VECTOR
     tuning = p.tuning if algo == _lib.FSB_SPMV_STREAM else (p.tuning & 0xFF if p.tuning & 0xFF in (2, 4, 8, 16, 32) else 0)
     with torch.cuda.device(dev):

@@ -120,6 +120,29 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
                          const int32_t* tile_row, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * y = A x from the "panel" regrouping of a CSR matrix (built once per matrix by the host code,
+ * flagsparse_b200/panel.py): entries grouped into units = (block of rb_rows rows) x (chunk of chunk_cols
+ * columns), row-major inside a unit, each unit cut into pieces of fsb_spmv_panel_piece_slots() slots so
+ * that no row's entries straddle two pieces.
+ *   val[s], rc[s]        per slot: value and packed word (local row << 16 | parity * chunk_cols + local
+ *                        column), parity = ordinal of the unit inside its row block modulo 2; unused
+ *                        slots carry local row 0xFFFF
+ *   unit_piece_ptr       pieces [unit_piece_ptr[u], unit_piece_ptr[u+1]) belong to unit u
+ *   unit_chunk           column chunk of unit u
+ *   rb_unit_ptr          units [rb_unit_ptr[b], rb_unit_ptr[b+1]) belong to row block b, in chunk order
+ * One CTA per row block keeps the block's y accumulators and two chunks of x in shared memory
+ * (fsb_spmv_panel_smem_bytes() must fit in 227 KiB; rb_rows < 65535).  Another stand-in for the launches of
+ * _triton_spmv_csr_impl_opt_prepared (spmv_csr.py:329-376), for matrices whose rows span few column chunks.
+ * status: optional device int32, set non-zero if a bounded wait on a bulk copy of x ran out.
+ */
+int fsb_spmv_panel_piece_slots(void);
+size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols);
+int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                       const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
+                       int32_t rb_rows, int32_t chunk_cols, const void* x, void* y, int64_t n_rows,
+                       int64_t n_cols, int32_t* status, void* stream);
+
+/*
  * y = A x with the STREAM algorithm for callers that must not (or cannot) allocate device memory: code
  * running inside a frozen or fixed-size memory pool, plugins that only ever receive buffers from their
  * host framework, latency-critical loops where cudaMalloc's device-wide synchronisation is unacceptable.

@@ -72,6 +72,44 @@ def test_edge_cases(cuda, fsb_lib, name, algo):
         assert np.all(y[np.asarray(lens) == 0] == 0)
 
 
+PANEL_CASES = ["one_row_one_entry", "one_row", "rows_31", "rows_32", "rows_33", "all_empty", "empty_then_full",
+               "single_entries", "more_rows_than_offsets_slots"]
+
+
+@pytest.mark.parametrize("name", PANEL_CASES)
+def test_panel_kernel_edge_cases(cuda, fsb_lib, name):
+    lens = _edge_cases()[name]
+    for n_cols in (5001, 1 << 17):  # a ragged last chunk of x, and many chunks
+        for vdt in (np.float32, np.float64):
+            data, idx, ptr = handmade_csr(17, lens, n_cols, vdt)
+            x = np.random.default_rng(18).uniform(-1, 1, n_cols).astype(vdt)
+            y = spmv(data, idx, ptr, (len(lens), n_cols), x, algo="panel")
+            assert_spmv_ok(y, data, idx, ptr, (len(lens), n_cols), x, what=f"panel/{name}")
+            assert np.all(y[np.asarray(lens) == 0] == 0)
+
+
+@pytest.mark.parametrize("vdt,idt", [("float32", "int32"), ("float64", "int64")])
+def test_panel_kernel_on_banded_matrix(cuda, fsb_lib, vdt, idt):
+    # 33M nnz in a band of +-16384 columns: large enough, and few enough column chunks per row block, for the
+    # panel layout to be chosen
+    spec = S.CsrSpec("band16k", 1 << 20, 1 << 20, ("poisson", 32.0), ("band", 16384), True, 0)
+    d, i, p = S.generate_csr(spec, "cuda:0", value_dtype=vdt, index_dtype=idt, indptr_dtype=idt)
+    x = S.dense_vector(spec, spec.n_cols, "cuda:0", value_dtype=vdt)
+    prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+    assert prep.algo == _lib.FSB_SPMV_PANEL and prep.panel is not None
+    # a band as wide as the matrix is short is not worth regrouping: the vector kernel stays
+    wide = S.config_spec("c2").scaled(1 << 18)
+    dw, iw, pw = S.generate_csr(wide, "cuda:0", value_dtype=vdt)
+    assert fs.prepare_spmv_csr(dw, iw, pw, (wide.n_rows, wide.n_cols)).algo == _lib.FSB_SPMV_VECTOR
+    del dw, iw, pw
+    y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    assert_spmv_ok(y.cpu().numpy(), d.cpu().numpy(), i.cpu().numpy(), p.cpu().numpy(), (spec.n_rows, spec.n_cols),
+                   x.cpu().numpy(), what="panel banded")
+    assert int(prep.panel.status.item()) == 0
+    assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)          # bit-reproducible
+    assert torch.equal(fs.flagsparse_spmv_csr(x=x * 4, prepared=prep), y * 4)  # exact under power-of-two scaling
+
+
 @pytest.mark.parametrize("tuning", STREAM_TUNINGS)
 def test_stream_tunings_stay_in_tolerance(cuda, fsb_lib, tuning):
     spec = S.config_spec("c3").scaled(1 << 15)
@@ -232,12 +270,14 @@ def test_config_c2_full_size(cuda, fsb_lib, vdt, idt):
     d, i, p = S.generate_csr(spec, "cuda:0", value_dtype=vdt, index_dtype=idt, indptr_dtype=idt)
     x = S.dense_vector(spec, spec.n_cols, "cuda:0", value_dtype=vdt)
     prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
-    assert prep.algo == _lib.FSB_SPMV_VECTOR  # uniform row lengths
+    assert prep.algo == _lib.FSB_SPMV_PANEL  # uniform row lengths inside a narrow band
     y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
     worst = check_spmv_blocks(spec, y, x.cpu().numpy(), sample_blocks(spec.n_rows, 24, 2048), vdt, idt, idt)
-    with env(FSB_SPMV_ALGO="stream"):
-        ys = fs.flagsparse_spmv_csr(d, i, p, x, (spec.n_rows, spec.n_cols))
-    check_spmv_blocks(spec, ys, x.cpu().numpy(), sample_blocks(spec.n_rows, 8, 2048, seed=1), vdt, idt, idt)
+    assert int(prep.panel.status.item()) == 0
+    for other in ("stream", "vector"):
+        with env(FSB_SPMV_ALGO=other):
+            ys = fs.flagsparse_spmv_csr(d, i, p, x, (spec.n_rows, spec.n_cols))
+        check_spmv_blocks(spec, ys, x.cpu().numpy(), sample_blocks(spec.n_rows, 8, 2048, seed=1), vdt, idt, idt)
     assert torch.equal(fs.flagsparse_spmv_csr(x=x * 2, prepared=prep), y * 2)
     assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)
     print(f"c2 {vdt}: nnz {d.numel()}, worst bound ratio {worst:.2e}")
