@@ -326,7 +326,13 @@ def run_ours(args, workload):
             nnz = d.numel()
             launches_per_step = 2 if prep.algo == _lib.FSB_SPMV_STREAM else 1
             si, sp_ = prep.kernel_indices.element_size(), prep.kernel_indptr.element_size()
-            extra["kernel"] = "stream" if prep.algo == _lib.FSB_SPMV_STREAM else "vector"
+            extra["kernel"] = prep.opt_buckets[0]["kind"]
+            if prep.panel is not None:
+                # bytes the panel kernel streams: entries (with padding), unit tables, x chunks, y
+                lay = prep.panel
+                extra["panel"] = {"rb_rows": lay.rb_rows, "chunk_cols": lay.chunk_cols, "units": lay.n_units,
+                                  "x_overhead": round(lay.x_overhead, 3), "slot_overhead": round(lay.slot_overhead, 3),
+                                  "layout_bytes": lay.nbytes()}
             my_rows = (0, spec.n_rows)
             run_y = lambda xv: fs.flagsparse_spmv_csr(x=xv, prepared=prep, out=out)  # noqa: E731
         else:

@@ -6,27 +6,28 @@
 // towards L2, so the product runs at the speed of the gathers, not of HBM.  Shared memory serves 32
 // scattered 4-byte reads per clock.  The prepare step therefore regroups the entries (once per matrix)
 // into units = (block of RB consecutive rows) x (chunk of CW consecutive columns); inside a unit the
-// entries keep their row-major order and are cut into pieces of 64 slots such that the entries of one row
-// never straddle two pieces (unused slots hold a sentinel).  An entry is a value plus one packed word
+// entries keep their row-major order and are cut into pieces of 512 slots such that the entries of one
+// row never straddle two pieces (unused slots hold a sentinel).  An entry is a value plus one packed word
 // (local row << 16 | buffer parity * CW + local column): 8 bytes for float32, the same as CSR with 32-bit
 // indices.  One CTA owns one row block:
 //   - the CW elements of x a unit needs arrive in shared memory by a cp.async.bulk copy (mbarrier
 //     completion), double-buffered so that the next unit's chunk is in flight while this one is used;
-//   - each warp takes whole pieces (fully coalesced 128-byte loads, several pieces in flight), multiplies
-//     with x from shared memory and adds the products to the row accumulators of the block, which also
-//     live in shared memory.  Entries of one row inside a 32-entry round are added in the order of their
-//     position (one pass per position in the run), rounds and pieces in program order, units in sequence
-//     with a CTA barrier in between: every sum is formed in one fixed order, so the result is
-//     bit-reproducible, and because a row occurs in one piece per unit no two warps update the same
-//     accumulator at the same time;
+//   - a warp takes a whole piece: lane l owns slots 16l .. 16l+15 (stored interleaved so that each 128-bit
+//     load of the warp is contiguous).  In round k every lane handles its k-th slot.  Two slots of one round are at least 16 positions apart,
+//     and a row has at most 16 entries in a unit (the prepare step refuses the matrix otherwise), so the
+//     32 lanes of a round always touch 32 different rows: each lane simply adds value * x[column] to its
+//     row's accumulator in shared memory, with no shuffles and no atomics.  Rounds follow each other in
+//     program order, a row lives in one piece per unit, and units are separated by a CTA barrier, so
+//     every accumulator receives its terms in one fixed order: the result is bit-reproducible;
 //   - after the last unit the accumulators are written to y, each row exactly once.
 #include "fsb_common.cuh"
 
 namespace fsb {
 
-constexpr int kPanelWarps = 16;
+constexpr int kPanelWarps = 32;
 constexpr int kPanelThreads = kPanelWarps * 32;
-constexpr int kPieceSlots = 64;
+constexpr int kPieceSlots = 512;   // 32 lanes x 16 rounds
+constexpr int kPieceRounds = 16;
 constexpr int kPanelWaitSpins = 1 << 22;
 constexpr uint32_t kNoRow = 0xFFFFu;
 
@@ -54,27 +55,54 @@ __device__ __forceinline__ bool p_wait_bounded(uint64_t* bar, uint32_t phase) {
   return false;
 }
 
-// one round: 32 consecutive slots of a piece, one per lane
-template <typename V>
-__device__ __forceinline__ void panel_round(V v, uint32_t w, const V* __restrict__ xs, V* __restrict__ y_part,
-                                            uint32_t col_mask, int lane) {
-  const uint32_t row = w >> 16;
-  const bool live = row != kNoRow;
-  const V p = live ? v * xs[w & col_mask] : (V)0;
-  const uint32_t prev = __shfl_up_sync(0xffffffffu, row, 1);
-  const bool head = (lane == 0) || (prev != row);
-  const uint32_t heads = __ballot_sync(0xffffffffu, head);
-  const int start = 31 - __clz(heads & (0xffffffffu >> (31 - lane)));  // first lane of this lane's run
-  const unsigned rank = (unsigned)(lane - start);
-  const unsigned max_rank = __reduce_max_sync(0xffffffffu, live ? rank : 0u);
-  for (unsigned j = 0; j <= max_rank; ++j) {
-    if (live && rank == j) y_part[row] += p;
-    __syncwarp();
+// G consecutive slots of one lane (rounds k0 .. k0+G-1 of the piece).  Products of one row are summed in a
+// register and added to the row's accumulator when the row ends (next_row is the row of the lane's next slot,
+// or kNoRow after its last one).  Within one round the 32 lanes are on 32 different rows; a row that spans two
+// lanes ends in the first of them at its last slot and in the second one earlier, i.e. in different rounds.
+template <typename V, int G>
+__device__ __forceinline__ void panel_rounds(const V (&v)[G], const uint32_t (&w)[G], uint32_t next_word, V& acc,
+                                             const V* __restrict__ xs, V* __restrict__ y_part, uint32_t col_mask) {
+#pragma unroll
+  for (int k = 0; k < G; ++k) {
+    const uint32_t row = w[k] >> 16;
+    const uint32_t next_row = (k + 1 < G ? w[k + 1] : next_word) >> 16;
+    const bool live = row != kNoRow;
+    if (live) acc += v[k] * xs[w[k] & col_mask];
+    if (live && next_row != row) {
+      y_part[row] += acc;
+      acc = (V)0;
+    }
+    __syncwarp();  // orders this round's accumulator updates before the next round's
+  }
+}
+
+// Storage inside a piece: slot (lane, k), k = 0..15, of the value array sits at (k / E) * 32 * E + lane * E + k % E
+// with E = elements per 16 bytes, and of the packed-word array at (k / 4) * 128 + lane * 4 + k % 4, so that every
+// 128-bit load of a warp reads 512 contiguous bytes.
+template <int G>
+__device__ __forceinline__ void ld_group(const float* piece, int lane, int g, float (&v)[G]) {
+  static_assert(G == 8, "float32 groups hold eight slots");
+  ld_stream4(piece + (2 * g) * 128 + lane * 4, *reinterpret_cast<float(*)[4]>(&v[0]));
+  ld_stream4(piece + (2 * g + 1) * 128 + lane * 4, *reinterpret_cast<float(*)[4]>(&v[4]));
+}
+template <int G>
+__device__ __forceinline__ void ld_group(const double* piece, int lane, int g, double (&v)[G]) {
+  static_assert(G == 4, "float64 groups hold four slots");
+  const double2 a = __ldcs(reinterpret_cast<const double2*>(piece + (2 * g) * 64 + lane * 2));
+  const double2 b = __ldcs(reinterpret_cast<const double2*>(piece + (2 * g + 1) * 64 + lane * 2));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <int G>
+__device__ __forceinline__ void ld_words(const uint32_t* piece, int lane, int g, uint32_t (&w)[G]) {
+#pragma unroll
+  for (int q = 0; q < G / 4; ++q) {
+    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece + (g * (G / 4) + q) * 128 + lane * 4));
+    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
   }
 }
 
 template <typename V>
-__global__ void __launch_bounds__(kPanelThreads, 2)
+__global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
                   const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
                   const V* __restrict__ x, V* __restrict__ y, int64_t n_rows, int64_t n_cols, int rb_rows,
@@ -125,32 +153,41 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
     // the other buffer was last read before the barrier that closed the previous unit: free to refill
     bool plain_next = false;
     if (u + 1 < u1) plain_next = load_chunk(unit_chunk[u + 1], b ^ 1);
-    if (!p_wait_bounded(&bars[b], (uint32_t)((ord >> 1) & 1))) s_failed = 1;
-    if (plain) __syncthreads();
-    const V* xb = xs;  // both buffers: the packed word carries the parity
     const int p_end = unit_piece_ptr[u + 1];
     int pc = unit_piece_ptr[u] + warp;
-    // four pieces per trip: sixteen 128-byte loads in flight per warp
-    for (; pc + 3 * kPanelWarps < p_end; pc += 4 * kPanelWarps) {
-      V v[8];
-      uint32_t w[8];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int64_t base = (int64_t)(pc + q * kPanelWarps) * kPieceSlots + lane;
-        v[2 * q] = ld_stream(val + base);
-        v[2 * q + 1] = ld_stream(val + base + 32);
-        w[2 * q] = ld_stream(rc + base);
-        w[2 * q + 1] = ld_stream(rc + base + 32);
-      }
-#pragma unroll
-      for (int q = 0; q < 8; ++q) panel_round<V>(v[q], w[q], xb, y_part, col_mask, lane);
+    constexpr int G = sizeof(V) == 4 ? 8 : 4;   // slots per load group
+    constexpr int NG = kPieceRounds / G;        // groups per piece
+    // the entries do not depend on x: start fetching the first group before waiting for the chunk
+    V v[G];
+    uint32_t w[G];
+    if (pc < p_end) {
+      ld_group<G>(val + (size_t)pc * kPieceSlots, lane, 0, v);
+      ld_words<G>(rc + (size_t)pc * kPieceSlots, lane, 0, w);
     }
-    for (; pc < p_end; pc += kPanelWarps) {
-      const int64_t base = (int64_t)pc * kPieceSlots + lane;
-      const V v0 = ld_stream(val + base), v1 = ld_stream(val + base + 32);
-      const uint32_t w0 = ld_stream(rc + base), w1 = ld_stream(rc + base + 32);
-      panel_round<V>(v0, w0, xb, y_part, col_mask, lane);
-      panel_round<V>(v1, w1, xb, y_part, col_mask, lane);
+    if (!p_wait_bounded(&bars[b], (uint32_t)((ord >> 1) & 1))) s_failed = 1;
+    if (plain) __syncthreads();
+    while (pc < p_end) {
+      V acc = (V)0;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        // next group (of this piece, or the first one of this warp's next piece) in flight while this one is used
+        V v2[G];
+        uint32_t w2[G];
+        const bool more = g + 1 < NG;
+        const int np = more ? pc : pc + kPanelWarps;
+        const bool have = np < p_end;
+        if (have) {
+          ld_group<G>(val + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, v2);
+          ld_words<G>(rc + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, w2);
+        }
+        const uint32_t next_word = more ? w2[0] : (kNoRow << 16);  // a lane's run ends with its last slot
+        panel_rounds<V, G>(v, w, next_word, acc, xs, y_part, col_mask);
+        if (have) {
+#pragma unroll
+          for (int k = 0; k < G; ++k) { v[k] = v2[k]; w[k] = w2[k]; }
+        }
+      }
+      pc += kPanelWarps;
     }
     __syncthreads();  // every add of this unit is done; its x buffer may be refilled
     if (s_failed) {
@@ -186,20 +223,18 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   if (!val || !rc || !unit_piece_ptr || !unit_chunk || !rb_unit_ptr || !x || !y) return FSB_EINVAL;
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols);
   if (smem > 227 * 1024) return FSB_ERANGE;
-  cudaError_t e;
-  if (vtype == FSB_F32) {
-    e = cudaFuncSetAttribute(spmv_panel_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_rc(e);
-    spmv_panel_kernel<float><<<(unsigned)n_row_blocks, kPanelThreads, smem, st>>>(
-        (const float*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const float*)x, (float*)y, n_rows, n_cols,
-        rb_rows, chunk_cols, status);
-  } else {
-    e = cudaFuncSetAttribute(spmv_panel_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_rc(e);
-    spmv_panel_kernel<double><<<(unsigned)n_row_blocks, kPanelThreads, smem, st>>>(
-        (const double*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const double*)x, (double*)y, n_rows, n_cols,
-        rb_rows, chunk_cols, status);
-  }
+  if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
+#define FSB_PANEL_LAUNCH(V)                                                                                   \
+  do {                                                                                                        \
+    cudaError_t e = cudaFuncSetAttribute(spmv_panel_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                          \
+    if (e != cudaSuccess) return cuda_rc(e);                                                                  \
+    spmv_panel_kernel<V><<<(unsigned)n_row_blocks, kPanelThreads, smem, st>>>(                                \
+        (const V*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const V*)x, (V*)y, n_rows, n_cols,       \
+        rb_rows, chunk_cols, status);                                                                         \
+  } while (0)
+  if (vtype == FSB_F32) FSB_PANEL_LAUNCH(float); else FSB_PANEL_LAUNCH(double);
+#undef FSB_PANEL_LAUNCH
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }

@@ -7,17 +7,19 @@ unit needs in shared memory.  It runs once per matrix, off the timed path, with 
 device; the product itself is one launch of fsb_spmv_csr_panel.
 """
 
+import os
+
 import torch
 
 from . import _lib
 from ._common import _VTYPE
 
 SM_COUNT_FALLBACK = 148
-CTAS_PER_SM = 2
+CTAS_PER_SM = 1              # one 1024-thread CTA (row block) per SM
 # the kernel is worth its second copy of the matrix only when the extra reads of x and the padding stay small
 MAX_X_OVERHEAD = 0.40       # bytes of x chunks loaded / bytes of entries streamed
 MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
-MAX_RUN = 32                # entries of one row inside one unit (they must fit one piece with room to spare)
+MAX_RUN = 16                # entries of one row inside one unit = rounds per piece (see csrc/spmv_panel.cu)
 MAX_ROW_NNZ = 512
 MIN_NNZ = 1 << 22
 NO_ROW = 0xFFFF
@@ -38,15 +40,19 @@ def _geometry(dtype, n_rows, device):
     L = _lib.lib()
     vt = _VTYPE[dtype]
     sv = 4 if dtype == torch.float32 else 8
-    chunk_cols = 4096 if sv == 4 else 2048
+    chunk_cols = int(os.environ.get("FSB_PANEL_CHUNK", "0")) or (8192 if sv == 4 else 4096)
     try:
         sms = torch.cuda.get_device_properties(device).multi_processor_count
     except Exception:
         sms = SM_COUNT_FALLBACK
     budget = (222 * 1024) // CTAS_PER_SM - 1024      # shared memory per CTA, two CTAs per SM
     fixed = int(L.fsb_spmv_panel_smem_bytes(vt, 0, chunk_cols))
-    rb_cap = min(32768, (budget - fixed) // sv // 64 * 64)
-    rb_rows = min(rb_cap, max(1024, -(-n_rows // (sms * CTAS_PER_SM))))  # one wave of CTAs when the matrix allows
+    rb_cap = min(49152, (budget - fixed) // sv // 64 * 64)
+    # whole waves of CTAs: the number of row blocks is a multiple of the CTAs the GPU runs at once
+    slots_gpu = sms * CTAS_PER_SM
+    n_blocks = max(1, -(-n_rows // rb_cap))
+    n_blocks = -(-n_blocks // slots_gpu) * slots_gpu
+    rb_rows = min(rb_cap, max(1024, -(-n_rows // n_blocks)))
     rb_rows = -(-rb_rows // 4) * 4
     return vt, sv, chunk_cols, rb_rows, int(L.fsb_spmv_panel_piece_slots())
 
@@ -139,7 +145,13 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
         return None
     piece = torch.searchsorted(piece_start, ar, right=True) - 1
     slot = ar - piece_start[piece]
-    pos = piece * SLOTS + slot
+    # inside a piece, slot = 16 * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
+    # contiguous: values at (k // E) * 32 * E + lane * E + k % E (E = values per 16 bytes), words with E = 4
+    lane_, k_ = slot >> 4, slot & 15
+    E = 16 // sv
+    pos_val = piece * SLOTS + (k_ // E) * (32 * E) + lane_ * E + k_ % E
+    pos = piece * SLOTS + (k_ >> 2) * 128 + lane_ * 4 + (k_ & 3)
+    del lane_, k_
     upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
     del j, run_id, new_run, cuts, piece_start, slot
     # ordinal of a unit inside its row block decides which of the two x buffers it uses
@@ -149,7 +161,8 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     field = (u_ord[unit_of_entry] & 1) * CW + (cols_p - (cols_p // CW) * CW)
     del rows_p, cols_p
     val = torch.zeros(n_pieces * SLOTS, dtype=data.dtype, device=dev)
-    val[pos] = data[perm]
+    val[pos_val] = data[perm]
+    del pos_val
     word = (rloc << 16) | field                         # fits 32 bits: local row < 65535
     word = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
     rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)

@@ -90,12 +90,15 @@ def test_panel_kernel_edge_cases(cuda, fsb_lib, name):
 
 @pytest.mark.parametrize("vdt,idt", [("float32", "int32"), ("float64", "int64")])
 def test_panel_kernel_on_banded_matrix(cuda, fsb_lib, vdt, idt):
-    # 33M nnz in a band of +-16384 columns: large enough, and few enough column chunks per row block, for the
-    # panel layout to be chosen
-    spec = S.CsrSpec("band16k", 1 << 20, 1 << 20, ("poisson", 32.0), ("band", 16384), True, 0)
+    # 33M nnz in a band of +-65536 columns over 2^20 rows: large enough, and few enough column chunks per row
+    # block, for the panel layout to be chosen
+    spec = S.config_spec("c2").scaled(1 << 20)
     d, i, p = S.generate_csr(spec, "cuda:0", value_dtype=vdt, index_dtype=idt, indptr_dtype=idt)
     x = S.dense_vector(spec, spec.n_cols, "cuda:0", value_dtype=vdt)
-    prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+    # float32 picks the panel layout by itself; float64 chunks of x are twice the bytes, which at this size
+    # is just over the overhead limit, so ask for it
+    with env(FSB_SPMV_ALGO=None if vdt == "float32" else "panel"):
+        prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
     assert prep.algo == _lib.FSB_SPMV_PANEL and prep.panel is not None
     # a band as wide as the matrix is short is not worth regrouping: the vector kernel stays
     wide = S.config_spec("c2").scaled(1 << 18)
