@@ -33,7 +33,7 @@ sys.path.insert(0, ROOT)
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures
 # summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {"c2": 1.113e9}  # profiles/spmv_stream_c2_f32.md
+NCU_TRAFFIC_BYTES = {"c2": 1.102e9}  # profiles/spmv_panel_c2_f32.md
 
 SPMV_WORKLOADS = {
     "c1": ("c1", "float32", "int32", "int32"),
@@ -412,7 +412,7 @@ def run_ours(args, workload):
             "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": NCU_TRAFFIC_BYTES.get(workload),
-                         "peak_source": f"{peak_kind} copy bandwidth per GPU", "per": "GPU, whole step (tile kernel + fix-up)"},
+                         "peak_source": f"{peak_kind} copy bandwidth per GPU", "per": "GPU, whole step (every kernel of the step)"},
             "setup_seconds": setup_s,
         }
         line.update(extra)
