@@ -118,11 +118,17 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
   constexpr int T = kThreads * IPT;
   constexpr int RC = T < 2048 ? T : 2048;  // offsets kept in shared memory per pass: RC + 1
   constexpr int LONG_CAP = T / 32 + 2;
+  constexpr int HUGE_LEN = 512;               // segments longer than this are summed by the whole CTA
+  constexpr int HUGE_CAP = T / HUGE_LEN + 2;
   constexpr int NW = kThreads / 32;
+  typedef typename Wide<V>::type W;
   __shared__ __align__(16) V s_prod[T];
   __shared__ int32_t s_off[RC + 1];
   __shared__ int32_t s_long[LONG_CAP];
+  __shared__ int32_t s_huge[HUGE_CAP];
+  __shared__ W s_part[HUGE_CAP][NW];
   __shared__ int s_nlong;
+  __shared__ int s_nhuge;
   __shared__ int s_head_partial;
 
   const int tid = threadIdx.x;
@@ -144,6 +150,24 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
     }
 #pragma unroll
     for (int k = 0; k < IPT; ++k) v[k] *= __ldg(x + (int64_t)c[k]);
+    if (rb == ra) {
+      // The whole tile lies inside one row (no row ends here): its sum is the carry.  Reduce straight from
+      // registers -- lane, then warp, then the eight warp sums in order -- and skip the staging altogether.
+      W acc = 0;
+#pragma unroll
+      for (int k = 0; k < IPT; ++k) acc += (W)v[k];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+      if ((tid & 31) == 0) s_part[0][tid >> 5] = acc;
+      __syncthreads();
+      if (tid == 0) {
+        W tot = 0;
+#pragma unroll
+        for (int q = 0; q < NW; ++q) tot += s_part[0][q];
+        carry[t] = (V)tot;
+      }
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < IPT / 4; ++j)
       st_shared4(&s_prod[(j * kThreads + tid) * 4], *reinterpret_cast<V(*)[4]>(&v[4 * j]));
@@ -165,7 +189,6 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
   const int grp = tid / L;
   const int ngrp = kThreads / L;
   const int long_len = 32 * L;
-  typedef typename Wide<V>::type W;
 
   for (int base = 0; base < nseg; base += RC) {
     const int m = (nseg - base) < RC ? (nseg - base) : RC;  // segments in this pass
@@ -180,7 +203,10 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
       }
       s_off[k] = o;
     }
-    if (tid == 0) s_nlong = 0;
+    if (tid == 0) {
+      s_nlong = 0;
+      s_nhuge = 0;
+    }
     __syncthreads();
 
     // pass 1: L lanes per segment
@@ -193,13 +219,16 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
         s = s_off[k];
         e = s_off[k + 1];
       }
-      const bool is_long = (L < 32) && (e - s > long_len);
+      const bool is_huge = e - s > HUGE_LEN;
+      const bool is_long = is_huge || ((L < 32) && (e - s > long_len));
       V acc = 0;
       if (!is_long)
         for (int p = s + lane; p < e; p += L) acc += s_prod[p];
       for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
       if (valid && lane == 0) {
-        if (is_long) {
+        if (is_huge) {
+          s_huge[atomicAdd(&s_nhuge, 1)] = k;
+        } else if (is_long) {
           s_long[atomicAdd(&s_nlong, 1)] = k;
         } else {
           const int g = base + k;
@@ -232,6 +261,34 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
         if (g == nrf) carry[t] = (V)acc;
         else if (g == 0 && s_head_partial) head[t] = (V)acc;
         else out.store((int64_t)ra + g, (V)acc);
+      }
+    }
+
+    // pass 3: segments of more than HUGE_LEN entries (at most a handful per tile): every warp sums one
+    // slice of each, then one thread per segment adds the warp sums in order
+    const int nhuge = s_nhuge;
+    if (nhuge > 0) {
+      for (int q = 0; q < nhuge; ++q) {
+        const int k = s_huge[q];
+        const int s = s_off[k], e = s_off[k + 1];
+        const int slice = (((e - s) + NW - 1) / NW + 31) & ~31;
+        const int b0 = s + w * slice;
+        const int b1 = (b0 + slice) < e ? (b0 + slice) : e;
+        W acc = 0;
+        for (int p = b0 + l32; p < b1; p += 32) acc += (W)s_prod[p];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+        if (l32 == 0) s_part[q][w] = acc;
+      }
+      __syncthreads();
+      if (tid < nhuge) {
+        W tot = 0;
+#pragma unroll
+        for (int q = 0; q < NW; ++q) tot += s_part[tid][q];
+        const int g = base + s_huge[tid];
+        if (g == nrf) carry[t] = (V)tot;
+        else if (g == 0 && s_head_partial) head[t] = (V)tot;
+        else out.store((int64_t)ra + g, (V)tot);
       }
     }
   }
