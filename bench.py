@@ -392,6 +392,23 @@ def run_ours(args, workload):
         t = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed, e2e_elapsed = float(t[0]), float(t[1])
+        if not args.no_single_gpu_baseline:
+            # the strong-scaling reference: the SAME matrix on one GPU (rank 0 alone; the others wait)
+            del op, d, i, p, step, run_y
+            torch.cuda.empty_cache()
+            if rank == 0:
+                d, i, p = S.generate_csr(spec, device, value_dtype=vdt, index_dtype=idt, indptr_dtype=pdt)
+                prep1 = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+                out1 = torch.empty(spec.n_rows, dtype=d.dtype, device=device)
+                step1 = lambda: fs.flagsparse_spmv_csr(x=x, prepared=prep1, out=out1)  # noqa: E731
+                for _ in range(3):
+                    step1()
+                n1 = max(3, min(args.steps, 50))
+                t1 = timed_region(torch, step1, n1, lambda: None) / n1
+                extra["single_gpu_same_workload"] = {"ms_per_step": t1 * 1e3, "value": nbytes / t1 / 1e9,
+                                                     "unit": "GB/s", "kernel": prep1.opt_buckets[0]["kind"],
+                                                     "steps": n1, "speedup_at_n_gpus": t1 / (elapsed / args.steps)}
+            dist.barrier()
     per_step = elapsed / args.steps
     value = nbytes / per_step / 1e9
     peak, peak_kind = measured_peak()
@@ -433,6 +450,8 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=("auto", "nccl", "peer"),
                     help="how the sharded run assembles y: NCCL all-gather, or peer stores fused into the kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-single-gpu-baseline", action="store_true",
+                    help="sharded runs: skip timing the same matrix on one GPU (rank 0) after the sharded measurement")
     args = ap.parse_args()
     workload = args.workload
     if workload == "auto":

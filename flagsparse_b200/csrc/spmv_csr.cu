@@ -28,16 +28,28 @@ constexpr int kThreads = 256;
 // ---------------------------------------------------------------------------------------------------
 template <typename V>
 struct LocalOut {
+  static constexpr bool kStaged = false;  // local stores of scattered rows are cheap enough
   V* y;
   __device__ __forceinline__ void store(int64_t i, V v) const { y[i] = v; }
+  // rows row0+first .. row0+last-1 from a shared-memory staging array, thread-strided
+  __device__ __forceinline__ void store_block(int64_t row0, const V* src, int first, int last, int tid) const {
+    for (int i = first + tid; i < last; i += kThreads) y[row0 + i] = src[i];
+  }
 };
 template <typename V>
 struct PeerOut {
+  static constexpr bool kStaged = true;   // every row goes to n_peers destinations: make the stores coalesced
   V* const* peers;
   int n_peers;
   int64_t row_offset;
   __device__ __forceinline__ void store(int64_t i, V v) const {
     for (int p = 0; p < n_peers; ++p) peers[p][row_offset + i] = v;
+  }
+  __device__ __forceinline__ void store_block(int64_t row0, const V* src, int first, int last, int tid) const {
+    for (int p = 0; p < n_peers; ++p) {
+      V* dst = peers[p] + row_offset + row0;
+      for (int i = first + tid; i < last; i += kThreads) dst[i] = src[i];
+    }
   }
 };
 
@@ -116,7 +128,9 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
                    const V* __restrict__ x, Out out, const int32_t* __restrict__ tile_row,
                    V* __restrict__ carry, V* __restrict__ head, int64_t nnz, int lane_shift) {
   constexpr int T = kThreads * IPT;
-  constexpr int RC = T < 2048 ? T : 2048;  // offsets kept in shared memory per pass: RC + 1
+  // segments handled per pass (offsets kept in shared memory: RC + 1); smaller where 48 KB would not hold it
+  constexpr int RC = (T >= 4096 && sizeof(V) == 8) ? 1024 : (T < 2048 ? T : 2048);
+  constexpr bool STAGED = Out::kStaged;  // collect finished rows in shared memory and write them out coalesced
   constexpr int LONG_CAP = T / 32 + 2;
   constexpr int HUGE_LEN = 512;               // segments longer than this are summed by the whole CTA
   constexpr int HUGE_CAP = T / HUGE_LEN + 2;
@@ -124,6 +138,7 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
   typedef typename Wide<V>::type W;
   __shared__ __align__(16) V s_prod[T];
   __shared__ int32_t s_off[RC + 1];
+  __shared__ V s_y[STAGED ? RC : 1];  // results of the rows that end in this tile (staged write-out only)
   __shared__ int32_t s_long[LONG_CAP];
   __shared__ int32_t s_huge[HUGE_CAP];
   __shared__ W s_part[HUGE_CAP][NW];
@@ -234,6 +249,7 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
           const int g = base + k;
           if (g == nrf) carry[t] = acc;
           else if (g == 0 && s_head_partial) head[t] = acc;
+          else if (STAGED) s_y[k] = acc;
           else out.store((int64_t)ra + g, acc);
         }
       }
@@ -260,6 +276,7 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
         const int g = base + k;
         if (g == nrf) carry[t] = (V)acc;
         else if (g == 0 && s_head_partial) head[t] = (V)acc;
+        else if (STAGED) s_y[k] = (V)acc;
         else out.store((int64_t)ra + g, (V)acc);
       }
     }
@@ -288,8 +305,17 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
         const int g = base + s_huge[tid];
         if (g == nrf) carry[t] = (V)tot;
         else if (g == 0 && s_head_partial) head[t] = (V)tot;
+        else if (STAGED) s_y[s_huge[tid]] = (V)tot;
         else out.store((int64_t)ra + g, (V)tot);
       }
+    }
+
+    // write-out: consecutive threads store consecutive rows (one request per 32 rows and destination)
+    if (STAGED) {
+      __syncthreads();
+      const int first = (base == 0 && s_head_partial) ? 1 : 0;   // row 0 of the tile is finished by the fix-up
+      const int last = (base + m) < nrf ? m : (nrf - base);       // the tail segment is not a row of this tile
+      out.store_block((int64_t)ra + base, s_y, first, last, tid);
     }
   }
 }

@@ -81,7 +81,9 @@ class ShardedCsrSpmv:
 
             self.prepared = prepare_spmv_csr(data, indices, indptr, (self.n_local, self.n_cols))
         if mode == "auto":
-            mode = "peer" if (local_spmv is None and self.world > 1 and self._stream_plan_ok()) else "nccl"
+            # the fused exchange needs the CUDA kernels, several ranks and something to multiply
+            fused_ok = local_spmv is None and self.world > 1 and data.is_cuda
+            mode = "peer" if fused_ok else "nccl"
         if mode not in ("nccl", "peer"):
             raise ValueError("mode must be 'auto', 'nccl' or 'peer'")
         if mode == "peer" and local_spmv is not None:
@@ -102,9 +104,6 @@ class ShardedCsrSpmv:
             pos += n
         if pos != self.n_rows:
             raise ValueError(f"row shards cover {pos} rows, the matrix has {self.n_rows}")
-
-    def _stream_plan_ok(self):
-        return self.prepared is not None and (self.prepared.tile_row is not None or self.prepared.data.numel() == 0)
 
     def _setup_peer(self):
         import torch.distributed._symmetric_memory as symm_mem
