@@ -380,10 +380,10 @@ static int run_vector(const void* data, const void* idx, const void* ptr, const 
                       int64_t n_rows, int64_t nnz, int tuning, cudaStream_t st) {
   int L = tuning & 0xff;
   if (L == 0) {
-    // about eight entries (two 4-element groups) per lane
+    // eight to sixteen entries (two to four 4-element groups) per lane: measured best on 32-entry rows
     const int64_t mean = n_rows > 0 ? nnz / n_rows : 0;
     L = 2;
-    while (L < 32 && 8 * L < mean + 3) L <<= 1;
+    while (L < 32 && 16 * L < mean + 3) L <<= 1;
   }
   if (n_rows * (int64_t)L / kThreads >= INT32_MAX) return FSB_ERANGE;
   switch (L) {
