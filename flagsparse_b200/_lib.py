@@ -41,7 +41,7 @@ SIGNATURES = {
     "fsb_spmv_csr": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp]),
     "fsb_spmv_csr_scatter": (
         _i32,
-        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp],
+        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp],
     ),
     "fsb_spmv_csr_noalloc": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
     "fsb_spmv_panel_piece_slots": (_i32, []),

@@ -61,11 +61,11 @@ struct PeerOut {
 //            requests per array instead of one per eight entries.
 //   otherwise: scalar loads, used when the arrays are not 16-byte aligned.
 // ---------------------------------------------------------------------------------------------------
-template <typename V, typename I, typename P, int L, bool ALIGNED>
+template <typename V, typename I, typename P, int L, bool ALIGNED, typename Out>
 __global__ void __launch_bounds__(kThreads) spmv_vector_kernel(const V* __restrict__ data,
                                                               const I* __restrict__ idx,
                                                               const P* __restrict__ ptr,
-                                                              const V* __restrict__ x, V* __restrict__ y,
+                                                              const V* __restrict__ x, Out out,
                                                               int64_t n_rows, int64_t nnz) {
   const int64_t gtid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
   const int64_t row = gtid / L;
@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(kThreads) spmv_vector_kernel(const V* __restri
   V acc = acc0 + acc1;
 #pragma unroll
   for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
-  if (lane == 0 && row < n_rows) y[row] = acc;
+  if (lane == 0 && row < n_rows) out.store(row, acc);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -362,21 +362,21 @@ static int ipt_of(int tuning) {
   }
 }
 
-template <typename V, typename I, typename P, int L>
-static void launch_vector(const void* data, const void* idx, const void* ptr, const void* x, void* y,
+template <typename V, typename I, typename P, int L, typename Out>
+static void launch_vector(const void* data, const void* idx, const void* ptr, const void* x, Out out,
                           int64_t n_rows, int64_t nnz, cudaStream_t st) {
   const int64_t threads = n_rows * L;
   const unsigned g = (unsigned)((threads + kThreads - 1) / kThreads);
   if (aligned_to(data, 16) && aligned_to(idx, 16))
-    spmv_vector_kernel<V, I, P, L, true><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
-                                                                 (const V*)x, (V*)y, n_rows, nnz);
+    spmv_vector_kernel<V, I, P, L, true, Out><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
+                                                                      (const V*)x, out, n_rows, nnz);
   else
-    spmv_vector_kernel<V, I, P, L, false><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
-                                                                  (const V*)x, (V*)y, n_rows, nnz);
+    spmv_vector_kernel<V, I, P, L, false, Out><<<g, kThreads, 0, st>>>((const V*)data, (const I*)idx, (const P*)ptr,
+                                                                       (const V*)x, out, n_rows, nnz);
 }
 
-template <typename V, typename I, typename P>
-static int run_vector(const void* data, const void* idx, const void* ptr, const void* x, void* y,
+template <typename V, typename I, typename P, typename Out>
+static int run_vector(const void* data, const void* idx, const void* ptr, const void* x, Out out,
                       int64_t n_rows, int64_t nnz, int tuning, cudaStream_t st) {
   int L = tuning & 0xff;
   if (L == 0) {
@@ -387,11 +387,11 @@ static int run_vector(const void* data, const void* idx, const void* ptr, const 
   }
   if (n_rows * (int64_t)L / kThreads >= INT32_MAX) return FSB_ERANGE;
   switch (L) {
-    case 2: launch_vector<V, I, P, 2>(data, idx, ptr, x, y, n_rows, nnz, st); break;
-    case 4: launch_vector<V, I, P, 4>(data, idx, ptr, x, y, n_rows, nnz, st); break;
-    case 8: launch_vector<V, I, P, 8>(data, idx, ptr, x, y, n_rows, nnz, st); break;
-    case 16: launch_vector<V, I, P, 16>(data, idx, ptr, x, y, n_rows, nnz, st); break;
-    case 32: launch_vector<V, I, P, 32>(data, idx, ptr, x, y, n_rows, nnz, st); break;
+    case 2: launch_vector<V, I, P, 2, Out>(data, idx, ptr, x, out, n_rows, nnz, st); break;
+    case 4: launch_vector<V, I, P, 4, Out>(data, idx, ptr, x, out, n_rows, nnz, st); break;
+    case 8: launch_vector<V, I, P, 8, Out>(data, idx, ptr, x, out, n_rows, nnz, st); break;
+    case 16: launch_vector<V, I, P, 16, Out>(data, idx, ptr, x, out, n_rows, nnz, st); break;
+    case 32: launch_vector<V, I, P, 32, Out>(data, idx, ptr, x, out, n_rows, nnz, st); break;
     default: return FSB_EINVAL;
   }
   FSB_RETURN_IF_LAUNCH_FAILED();
@@ -450,8 +450,14 @@ struct SpmvArgs {
 
 template <typename V, typename I, typename P>
 static int spmv_typed(const SpmvArgs& a) {
-  if (a.algo == FSB_SPMV_VECTOR)
-    return run_vector<V, I, P>(a.data, a.idx, a.ptr, a.x, a.y, a.n_rows, a.nnz, a.tuning, a.st);
+  if (a.algo == FSB_SPMV_VECTOR) {
+    if (a.y_peers) {
+      PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset};
+      return run_vector<V, I, P, PeerOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.n_rows, a.nnz, a.tuning & 0xff, a.st);
+    }
+    LocalOut<V> out{(V*)a.y};
+    return run_vector<V, I, P, LocalOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.n_rows, a.nnz, a.tuning, a.st);
+  }
   if (a.y_peers) {
     PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset};
     return run_stream<V, I, P, PeerOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.tile_row, a.scratch, a.nnz,
@@ -536,7 +542,7 @@ extern "C" int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, c
 
 extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
                                     const void* indptr, const void* x, void* const* y_peers, int n_peers,
-                                    int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                                    int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int algo,
                                     int tuning, const int32_t* tile_row, void* scratch, size_t scratch_bytes,
                                     void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
@@ -555,11 +561,15 @@ extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void*
     FSB_RETURN_IF_LAUNCH_FAILED();
     return FSB_OK;
   }
-  if (tile_row == nullptr || scratch == nullptr) return FSB_EINVAL;
-  if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
-  if (!aligned_to(scratch, 16)) return FSB_EALIGN;
+  if (algo == FSB_SPMV_AUTO) algo = (tile_row != nullptr && scratch != nullptr) ? FSB_SPMV_STREAM : FSB_SPMV_VECTOR;
+  if (algo != FSB_SPMV_VECTOR && algo != FSB_SPMV_STREAM) return FSB_EINVAL;
+  if (algo == FSB_SPMV_STREAM) {
+    if (tile_row == nullptr || scratch == nullptr) return FSB_EINVAL;
+    if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
+    if (!aligned_to(scratch, 16)) return FSB_EALIGN;
+  }
   SpmvArgs a{data, indices, indptr, x, nullptr, y_peers, n_peers, row_offset, n_rows, nnz,
-             FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
+             algo, tuning, tile_row, scratch, st};
   return spmv_dispatch(vtype, itype, ptype, a);
 }
 

@@ -108,17 +108,9 @@ class ShardedCsrSpmv:
     def _setup_peer(self):
         import torch.distributed._symmetric_memory as symm_mem
 
-        if self.prepared.tile_row is None and self.prepared.data.numel() > 0:
-            # small shards pick the vector kernel; the fused exchange needs the tiled one
-            from .spmv_csr import _tile_plan
-
-            L = _lib.lib()
-            p = self.prepared
-            vt = _VTYPE[p.data.dtype]
-            p.tile_nnz = int(L.fsb_spmv_tile_nnz(vt, p.tuning))
-            p.tile_row = _tile_plan(p.kernel_indptr, p.n_rows, p.data.numel(), p.tile_nnz)
-            p.scratch = torch.empty(int(L.fsb_spmv_csr_scratch_bytes(vt, p.data.numel(), p.tuning)),
-                                    dtype=torch.uint8, device=p.data.device)
+        # the epilogue with peer stores exists for the vector and the stream kernel; a shard prepared for the
+        # panel kernel uses the vector kernel here (its rows are uniform by construction)
+        self._peer_algo = _lib.FSB_SPMV_STREAM if self.prepared.algo == _lib.FSB_SPMV_STREAM else _lib.FSB_SPMV_VECTOR
         group = self.group if self.group is not None else dist.group.WORLD
         # two result buffers used alternately: a rank may start the next product while its peers still
         # read the previous one, so a single barrier per product is enough
@@ -174,7 +166,7 @@ class ShardedCsrSpmv:
                     _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
                     _ptr(p.data), _ptr(p.kernel_indices), p.kernel_indptr.data_ptr(), _ptr(x),
                     self._peer_ptrs.data_ptr(), self.world, base + self.row_start, p.n_rows, p.n_cols, p.data.numel(),
-                    p.tuning, None if p.tile_row is None else p.tile_row.data_ptr(),
+                    self._peer_algo, p.tuning if self._peer_algo == _lib.FSB_SPMV_STREAM else 0, None if p.tile_row is None else p.tile_row.data_ptr(),
                     None if p.scratch is None else p.scratch.data_ptr(),
                     0 if p.scratch is None else p.scratch.numel(), _stream_ptr(self.device),
                 )

@@ -111,12 +111,13 @@ int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, const void* 
  * Same product, but every finished y value is stored into n_peers output vectors (one per GPU of the
  * box, the local one included) through peer-mapped pointers, at element offset row_offset + i: the
  * SpMV epilogue doubles as the all-gather of the row-sharded driver.  y_peers is a DEVICE array of
- * n_peers pointers.  Always uses the STREAM algorithm.  The reference has no multi-GPU path; this
+ * n_peers pointers.  algo: FSB_SPMV_VECTOR (no plan, no scratch) or FSB_SPMV_STREAM, as for fsb_spmv_csr;
+ * FSB_SPMV_AUTO takes STREAM when tile_row and scratch are given.  The reference has no multi-GPU path; this
  * stands in for "each rank runs spmv_csr.py:329-376 on its row shard, then y is all-gathered".
  */
 int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
                          const void* indptr, const void* x, void* const* y_peers, int n_peers,
-                         int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int tuning,
+                         int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int algo, int tuning,
                          const int32_t* tile_row, void* scratch, size_t scratch_bytes, void* stream);
 
 /*

@@ -44,18 +44,25 @@ def _worker(rank, world, port, result_dir):
         d, i, p = S.generate_csr(spec, device, indptr_dtype="int64", row_range=(r0, r1))
         x = S.dense_vector(spec, spec.n_cols, device)
         results = {}
-        for mode in ("nccl", "peer"):
-            op = ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=mode)
+        # the peer-store epilogue exists for the vector kernel (picked for these uniform rows) and the stream kernel
+        for mode, algo in (("nccl", None), ("peer", None), ("peer", "stream")):
+            if algo:
+                os.environ["FSB_SPMV_ALGO"] = algo
+            try:
+                op = ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=mode)
+            finally:
+                os.environ.pop("FSB_SPMV_ALGO", None)
             y = None
             for rep in range(3):
                 y = op.matvec(x * float(rep + 1))
             torch.cuda.synchronize()
-            results[mode] = y.clone()
-        # the two modes may run different kernels (different order of additions): each is held to the
-        # oracle bound by the parent; here only that they agree closely
-        assert torch.allclose(results["nccl"], results["peer"], rtol=1e-4, atol=1e-4)
-        np.save(os.path.join(result_dir, f"y{rank}.npy"), results["peer"].cpu().numpy())
-        np.save(os.path.join(result_dir, f"n{rank}.npy"), results["nccl"].cpu().numpy())
+            results[(mode, algo)] = y.clone()
+        # vector kernel with local stores and with peer stores: the same sums, the same bits
+        assert torch.equal(results[("nccl", None)], results[("peer", None)])
+        # the stream kernel adds in another order: held to the oracle bound by the parent, close to the others here
+        assert torch.allclose(results[("nccl", None)], results[("peer", "stream")], rtol=1e-4, atol=1e-4)
+        np.save(os.path.join(result_dir, f"y{rank}.npy"), results[("peer", None)].cpu().numpy())
+        np.save(os.path.join(result_dir, f"n{rank}.npy"), results[("peer", "stream")].cpu().numpy())
     finally:
         dist.destroy_process_group()
 
@@ -76,5 +83,5 @@ def test_two_ranks_nccl_and_peer(cuda, fsb_lib, tmp_path):
     spec = S.config_spec("c5").scaled(1 << 18)
     d, i, p = S.generate_csr(spec, None, indptr_dtype="int64")
     x = S.dense_vector(spec, spec.n_cols) * np.float32(3.0)
-    assert_spmv_ok(y0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores")
-    assert_spmv_ok(n0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, nccl")
+    assert_spmv_ok(y0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores, vector kernel")
+    assert_spmv_ok(n0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores, stream kernel")
