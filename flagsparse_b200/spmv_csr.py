@@ -173,6 +173,12 @@ def _validate_spmv_x(x, prepared):
 
 def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=None):
     """Analyse a CSR matrix once for repeated SpMV calls (reference: spmv_csr.py:455-495)."""
+    return _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected=True)
+
+
+def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected):
+    """reuse_expected=False (a one-shot product) skips the panel regrouping, which costs about as much as a
+    hundred products and only pays when the prepared matrix is used again."""
     data, kernel_indices, kernel_indptr, n_rows, n_cols, stats = _prepare_spmv_csr_matrix(
         data, indices, indptr, shape
     )
@@ -184,7 +190,8 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     tile_nnz, tile_row, scratch, panel_layout = 0, None, None, None
     # rows of about equal length whose columns stay within a few chunks: regroup once, keep x in shared memory
     want_panel = algo == _lib.FSB_SPMV_PANEL or (
-        algo == _lib.FSB_SPMV_VECTOR and os.environ.get("FSB_SPMV_ALGO", "") == "" and _PANEL_ENABLED)
+        reuse_expected and algo == _lib.FSB_SPMV_VECTOR and os.environ.get("FSB_SPMV_ALGO", "") == ""
+        and _PANEL_ENABLED)
     if want_panel:
         from . import panel
 
@@ -245,7 +252,7 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
     if prepared is None:
         if any(arg is None for arg in (data, indices, indptr, shape)):
             raise ValueError("data, indices, indptr, and shape are required when prepared is not provided")
-        prepared = prepare_spmv_csr(data, indices, indptr, shape, block_nnz=block_nnz, max_segments=max_segments)
+        prepared = _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected=False)
     x = _validate_spmv_x(x, prepared)
     dev = prepared.data.device
     dtype = prepared.data.dtype
