@@ -33,7 +33,12 @@ sys.path.insert(0, ROOT)
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures
 # summarised under profiles/ (None until a capture exists for the workload)
-NCU_TRAFFIC_BYTES = {"c2": 1.102e9}  # profiles/spmv_panel_c2_f32.md
+NCU_TRAFFIC_BYTES = {
+    "c2": 1.102e9,      # profiles/spmv_panel_c2_f32.md
+    "c3": 3.534e9,      # profiles/spmv_stream_c3_f32.md
+    "c4n32": 1.290e9,   # profiles/spmm_tile_c4_f32.md
+    "c4n128": 7.951e9,  # profiles/spmm_tile_c4_f32.md
+}
 
 SPMV_WORKLOADS = {
     "c1": ("c1", "float32", "int32", "int32"),
@@ -261,6 +266,57 @@ def timed_region(torch, fn, steps, barrier):
     return start.elapsed_time(end) / 1e3  # seconds
 
 
+def timed_pipeline(torch, api_call, host_in, host_out, steps, depth=2):
+    """End-to-end steps with the three stages of consecutive steps overlapped: copy-in of step k+1, the product
+    of step k and copy-out of step k-1 run on three streams with `depth` device buffers each.  Every step still
+    moves its own input from pinned host memory and its own result back inside the timed region.
+    api_call(dev_in, dev_out) is the package's public call, issued on the current (compute) stream."""
+    dev = torch.cuda.current_device()
+    s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dev_in = [torch.empty(host_in.shape, dtype=host_in.dtype, device="cuda") for _ in range(depth)]
+    dev_out = [torch.empty(host_out.shape, dtype=host_out.dtype, device="cuda") for _ in range(depth)]
+    ev_in = [torch.cuda.Event() for _ in range(depth)]      # input b is on the device
+    ev_used = [torch.cuda.Event() for _ in range(depth)]    # input b has been consumed
+    ev_res = [torch.cuda.Event() for _ in range(depth)]     # result b is ready
+    ev_read = [torch.cuda.Event() for _ in range(depth)]    # result b has been copied out
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    main = torch.cuda.current_stream()
+
+    def run(n):
+        for k in range(n):
+            b = k % depth
+            with torch.cuda.stream(s_in):
+                if k >= depth:
+                    s_in.wait_event(ev_used[b])
+                dev_in[b].copy_(host_in, non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[b])
+                if k >= depth:
+                    s_run.wait_event(ev_read[b])
+                api_call(dev_in[b], dev_out[b])
+                ev_used[b].record(s_run)
+                ev_res[b].record(s_run)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_res[b])
+                host_out.copy_(dev_out[b], non_blocking=True)
+                ev_read[b].record(s_out)
+
+    run(2 * depth)  # warm-up of the pipeline
+    torch.cuda.synchronize()
+    start.record(main)
+    for st in (s_in, s_run, s_out):
+        st.wait_event(start)
+    run(steps)
+    for st in (s_in, s_run, s_out):
+        fin = torch.cuda.Event()
+        fin.record(st)
+        main.wait_event(fin)
+    end.record(main)
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / 1e3
+
+
 def run_ours(args, workload):
     import torch
     import torch.distributed as dist
@@ -313,6 +369,8 @@ def run_ours(args, workload):
             dev_in.copy_(host_in, non_blocking=True)
             c = fs.flagsparse_spmm_csr_opt(B=dev_in, prepared=prep, out=out)
             host_out.copy_(c, non_blocking=True)
+
+        api_call = lambda di, do: fs.flagsparse_spmm_csr_opt(B=di, prepared=prep, out=do)  # noqa: E731
     else:
         cfg, vdt, idt, pdt = SPMV_WORKLOADS[workload]
         spec = S.config_spec(cfg)
@@ -335,6 +393,7 @@ def run_ours(args, workload):
                                   "layout_bytes": lay.nbytes()}
             my_rows = (0, spec.n_rows)
             run_y = lambda xv: fs.flagsparse_spmv_csr(x=xv, prepared=prep, out=out)  # noqa: E731
+            api_call = lambda di, do: fs.flagsparse_spmv_csr(x=di, prepared=prep, out=do)  # noqa: E731
         else:
             # every rank derives the row lengths (a pure function of the row index), hence the same partition
             if spec.dedup:
@@ -387,6 +446,10 @@ def run_ours(args, workload):
     for _ in range(3):
         e2e_step()
     e2e_elapsed = timed_region(torch, e2e_step, args.steps, barrier)
+    e2e_serial = e2e_elapsed
+    if world == 1:
+        # the same end-to-end step with copy-in, product and copy-out of consecutive steps overlapped
+        e2e_elapsed = min(e2e_serial, timed_pipeline(torch, api_call, host_in, host_out, args.steps))
 
     if world > 1:
         t = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
@@ -424,7 +487,10 @@ def run_ours(args, workload):
             "frac_of_nominal_8tbs": value / (8000.0 * world),
             "e2e": {"value": nbytes / (e2e_elapsed / args.steps) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_elapsed / args.steps * 1e3},
+                    "ms_per_step": e2e_elapsed / args.steps * 1e3,
+                    "serial_ms_per_step": e2e_serial / args.steps * 1e3,
+                    "how": ("copy-in, product and copy-out of consecutive steps overlapped on three streams"
+                            if e2e_elapsed < e2e_serial else "copy-in, product, copy-out one after the other")},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
