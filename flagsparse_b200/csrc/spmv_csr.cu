@@ -153,7 +153,29 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
   const int32_t ra = tile_row[t];
   const int32_t rb = tile_row[t + 1];
 
-  // ---- A: products into shared memory ------------------------------------------------------------
+  // segments = rows ending here (ra..rb-1) + the row that continues (tail)
+  const int nrf = rb - ra;
+  const int nseg = nrf + 1;
+  // offsets of the segments [base, base + m] of this tile, relative to the tile, into shared memory
+  auto load_offsets = [&](int base, int m) {
+    for (int k = tid; k <= m; k += kThreads) {
+      const int g = base + k;  // offset entry g: start of segment g
+      int32_t o = cnt;         // g == nseg: end of the tail segment
+      if (g <= nrf) {
+        const int64_t d = (int64_t)ptr[(int64_t)ra + g] - lo;
+        o = d < 0 ? 0 : (d > cnt ? cnt : (int32_t)d);
+        if (g == 0) s_head_partial = (d < 0 && nrf > 0) ? 1 : 0;
+      }
+      s_off[k] = o;
+    }
+    if (tid == 0) {
+      s_nlong = 0;
+      s_nhuge = 0;
+    }
+  };
+  const int m0 = nseg < RC ? nseg : RC;
+
+  // ---- A: products into shared memory (the first pass of offsets is fetched while the gathers fly) -----
   if (VEC && cnt == T) {
     V v[IPT];
     I c[IPT];
@@ -163,6 +185,7 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
       ld_stream4(data + e, *reinterpret_cast<V(*)[4]>(&v[4 * j]));
       ld_stream4(idx + e, *reinterpret_cast<I(*)[4]>(&c[4 * j]));
     }
+    if (rb != ra) load_offsets(0, m0);
 #pragma unroll
     for (int k = 0; k < IPT; ++k) v[k] *= __ldg(x + (int64_t)c[k]);
     if (rb == ra) {
@@ -187,13 +210,12 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
     for (int j = 0; j < IPT / 4; ++j)
       st_shared4(&s_prod[(j * kThreads + tid) * 4], *reinterpret_cast<V(*)[4]>(&v[4 * j]));
   } else {
+    load_offsets(0, m0);
     for (int e = tid; e < cnt; e += kThreads)
       s_prod[e] = ld_stream(data + lo + e) * __ldg(x + (int64_t)ld_stream(idx + lo + e));
   }
 
-  // ---- B/C: segments = rows ending here (ra..rb-1) + the row that continues (tail) ---------------
-  const int nrf = rb - ra;
-  const int nseg = nrf + 1;
+  // ---- C: segmented reduction ------------------------------------------------------------------------
   int L;
   {
     const int mean = cnt / nseg;
@@ -207,22 +229,11 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
 
   for (int base = 0; base < nseg; base += RC) {
     const int m = (nseg - base) < RC ? (nseg - base) : RC;  // segments in this pass
-    __syncthreads();  // products visible; previous pass done with s_off / s_long
-    for (int k = tid; k <= m; k += kThreads) {
-      const int g = base + k;  // offset entry g: start of segment g
-      int32_t o = cnt;         // g == nseg: end of the tail segment
-      if (g <= nrf) {
-        const int64_t d = (int64_t)ptr[(int64_t)ra + g] - lo;
-        o = d < 0 ? 0 : (d > cnt ? cnt : (int32_t)d);
-        if (g == 0) s_head_partial = (d < 0 && nrf > 0) ? 1 : 0;
-      }
-      s_off[k] = o;
+    if (base > 0) {
+      __syncthreads();  // previous pass done with s_off / s_long / s_huge
+      load_offsets(base, m);
     }
-    if (tid == 0) {
-      s_nlong = 0;
-      s_nhuge = 0;
-    }
-    __syncthreads();
+    __syncthreads();  // products and offsets visible
 
     // pass 1: L lanes per segment
     const int iters = (m + ngrp - 1) / ngrp;
@@ -405,7 +416,7 @@ static int launch_stream(const void* data, const void* idx, const void* ptr, con
   const int64_t n_tiles = (nnz + T - 1) / T;
   V* carry = (V*)scratch;
   V* head = carry + n_tiles;
-  int shift = (tuning & 0xff) ? (tuning & 0xff) - 1 : 2;
+  int shift = (tuning & 0xff) ? (tuning & 0xff) - 1 : 3;
   if (shift > 16) shift = 16;
   const bool vec = aligned_to(data, 16) && aligned_to(idx, 16);
   if (vec)
