@@ -301,3 +301,25 @@ def test_config_c3_full_size(cuda, fsb_lib):
     assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)
     assert int(lens.max()) > 60000
     print(f"c3: nnz {d.numel()}, longest row {int(lens.max())}, worst bound ratio {worst:.2e}")
+
+
+def test_more_than_2_31_entries(cuda, fsb_lib):
+    """A matrix whose nnz does not fit int32 (2^26 rows, Poisson(34) rows, 2.28e9 entries, int64 indptr): both
+    kernels against host-regenerated row blocks, including blocks whose offsets lie beyond 2^31."""
+    if torch.cuda.get_device_properties(0).total_memory < 60 * 2**30:
+        pytest.skip("needs about 40 GB of device memory")
+    spec = S.CsrSpec("c5x", 1 << 26, 1 << 26, ("poisson", 34.0), ("band", 1 << 20), False, 0)
+    d, i, p = S.generate_csr(spec, "cuda:0", indptr_dtype="int64")
+    nnz = d.numel()
+    assert nnz > 2**31 and p.dtype == torch.int64 and int(p[-1]) == nnz
+    x = S.dense_vector(spec, spec.n_cols, "cuda:0")
+    xn = x.cpu().numpy()
+    blocks = sample_blocks(spec.n_rows, 6, 2048) + [(spec.n_rows - 4096, spec.n_rows), (63_500_000, 63_502_048)]
+    assert int(p[63_500_000]) > 2**31 - 2**27  # around and past the int32 boundary
+    for algo in ("vector", "stream"):
+        with env(FSB_SPMV_ALGO=algo):
+            prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+            assert prep.kernel_indptr.dtype == torch.int64
+            y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
+        check_spmv_blocks(spec, y, xn, blocks, indptr_dtype="int64")
+        del prep, y
