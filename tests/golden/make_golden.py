@@ -159,7 +159,7 @@ def host_helper_goldens(R, M):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from flagsparse.sparse_operations import spmm_csr as M  # noqa: E402
