@@ -6,6 +6,7 @@ row-major B.  Compute goes through libfsb.so (include/fsb.h); there is no Triton
 """
 
 from ._common import SUPPORTED_INDEX_DTYPES, SUPPORTED_VALUE_DTYPES, _tolerance_for_dtype
+from .coo import PreparedCoo, flagsparse_spmm_coo, flagsparse_spmv_coo, prepare_spmv_coo
 from .sharded import ShardedCsrSpmv, partition_rows_by_nnz
 from .spmm_csr import (
     PreparedCsrSpmmOpt,
@@ -31,6 +32,10 @@ __all__ = [
     "coo_to_csr_for_spmv",
     "prepare_spmv_coo_tocsr",
     "flagsparse_spmv_coo_tocsr",
+    "PreparedCoo",
+    "prepare_spmv_coo",
+    "flagsparse_spmv_coo",
+    "flagsparse_spmm_coo",
     "PreparedCsrSpmmOpt",
     "prepare_spmm_csr_opt",
     "flagsparse_spmm_csr",

@@ -11,8 +11,12 @@ the reference's @triton.jit kernels:
   SpMV opt path   _triton_spmv_csr_impl_opt_prepared  (:329-376) with _build_spmv_opt_buckets (:281-327)
   SpMM base path  _triton_spmm_csr_impl               (src/flagsparse/sparse_operations/spmm_csr.py:525-599)
   SpMM opt path   _run_spmm_opt_bucket / _run_spmm_opt_split_bucket (:922-1030), driven as in :1046-1055
+  COO SpMV       _triton_spmv_coo_kernel             (src/flagsparse/sparse_operations/spmv_coo.py:252-289), on
+                 a PreparedCoo built as _prepare_coo_tensors (:183-222) builds it, row-run and atomic forms
+  COO SpMM       _triton_spmm_coo_impl               (src/flagsparse/sparse_operations/spmm_coo.py:533-570) after
+                 _prepare_spmm_coo_canonical_prepared (:78-105), as _run_spmm_coo_route (:626-668) does
 plus the pure host helpers (_resolve_spmm_alg1_launch_config, _select_spmm_opt_block_n,
-coo_to_csr_for_spmv).  Inputs and outputs are stored together, so the fixtures stay valid even if the
+coo_to_csr_for_spmv).  `--only coo` regenerates the COO fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
 synthetic generator changes.  Nothing here is imported by the package, the tests or the benchmark.
 """
 
@@ -135,6 +139,57 @@ def run_reference_spmm(M, data, indices, indptr, shape, B):
     return C_base.numpy(), C_opt.numpy(), meta
 
 
+def coo_cases():
+    """Unsorted entries with duplicate (row, col) pairs and rows without entries."""
+    out = {}
+    for name, seed, n_rows, n_cols, nnz, vt, rt, ct, n_dense in (
+            ("dups_f32", 31, 37, 29, 400, np.float32, np.int64, np.int32, 5),
+            ("dups_f64", 32, 64, 300, 500, np.float64, np.int32, np.int64, 32),
+            ("sparse_rows_f32", 33, 200, 64, 90, np.float32, np.int32, np.int32, 12)):
+        rng = np.random.default_rng(seed)
+        row = rng.integers(0, n_rows, nnz).astype(rt)
+        row[row % 5 == 3] = 1  # a long row and a set of rows that stay empty
+        col = rng.integers(0, n_cols, nnz).astype(ct)
+        val = rng.uniform(-1, 1, nnz).astype(vt)
+        x = rng.uniform(-1, 1, n_cols).astype(vt)
+        B = rng.uniform(-1, 1, (n_cols, n_dense)).astype(vt)
+        out[name] = (val, row, col, (n_rows, n_cols), x, B)
+    return out
+
+
+def run_reference_coo(V, MC, val, row, col, shape, x, B):
+    n_rows, n_cols = shape
+    val, row, col, x, B = _t(val), _t(row), _t(col), _t(x), _t(B)
+    # SpMV, sort_by_row=True (row-run kernel) and False (atomic kernel): _prepare_coo_tensors minus is_cuda
+    d, r64, c64 = V._sort_coo_lex_inplace(val, row, col, n_cols)
+    seg = V._seg_starts_from_sorted_rows(r64.to(torch.int32), d.numel(), d.device)
+    p_seg = V.PreparedCoo(d, r64.to(torch.int32), c64.to(torch.int32), shape, seg_starts=seg)
+    y_seg = V._triton_spmv_coo_kernel(p_seg, x, block_size=256, num_warps=4, block_inner=128)
+    p_at = V.PreparedCoo(val.contiguous(), row.to(torch.int32), col.to(torch.int32), shape, seg_starts=None)
+    y_atomic = V._triton_spmv_coo_kernel(p_at, x, block_size=256, num_warps=4, block_inner=128)
+    # SpMM, as _run_spmm_coo_route: coalesce + sort, then the row-run kernel
+    kr = row.to(torch.int32)
+    kc = col.to(torch.int32)
+    n_dense = int(B.shape[1])
+    (cd, cr, cc, cB, _, _, _, out_dtype, _) = MC._prepare_spmm_coo_canonical_prepared(val, kr, kc, B, n_rows, n_cols,
+                                                                                      n_dense)
+    launch = MC._resolve_spmm_coo_launch_config(n_dense, cd.numel())
+    C = MC._triton_spmm_coo_impl(cd, cr, cc, cB, n_rows, n_dense, block_n=launch["block_n"],
+                                 block_nnz=launch["block_nnz"], route="rowrun", output_dtype=out_dtype)
+    return (y_seg.numpy(), y_atomic.numpy(), C.numpy(), d.numpy(), r64.numpy(), c64.numpy(), seg.numpy(), launch)
+
+
+def make_coo(index, V, MC):
+    index["coo"] = {}
+    for name, (val, row, col, shape, x, B) in coo_cases().items():
+        y_seg, y_atomic, C, d, r, c, seg, launch = run_reference_coo(V, MC, val, row, col, shape, x, B)
+        np.savez_compressed(os.path.join(HERE, f"coo_{name}.npz"), data=val, row=row, col=col, shape=np.asarray(shape),
+                            x=x, B=B, y_seg=y_seg, y_atomic=y_atomic, C=C, sorted_data=d, sorted_row=r, sorted_col=c,
+                            seg_starts=seg)
+        index["coo"][name] = {"nnz": int(val.size), "n_segs": int(seg.size - 1), "launch": launch}
+        print("coo", name, val.size, index["coo"][name], flush=True)
+
+
 def host_helper_goldens(R, M):
     g = {"alg1": [], "opt_block_n": {}, "coo": {}}
     for n in (1, 4, 5, 8, 9, 16, 17, 24, 32, 33, 48, 64, 65, 96, 128, 256):
@@ -160,11 +215,22 @@ def host_helper_goldens(R, M):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
+    ap.add_argument("--only", choices=("all", "coo"), default="all")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
+    from flagsparse.sparse_operations import spmm_coo as MC  # noqa: E402
     from flagsparse.sparse_operations import spmm_csr as M  # noqa: E402
+    from flagsparse.sparse_operations import spmv_coo as V  # noqa: E402
     from flagsparse.sparse_operations import spmv_csr as R  # noqa: E402
 
+    index_path = os.path.join(HERE, "index.json")
+    if args.only == "coo":
+        with open(index_path) as f:
+            index = json.load(f)
+        make_coo(index, V, MC)
+        with open(index_path, "w") as f:
+            json.dump(index, f, indent=1, sort_keys=True)
+        return
     index = {"spmv": {}, "spmm": {}}
     for name, ((data, indices, indptr), shape, x) in spmv_cases().items():
         y_base, y_opt, meta = run_reference_spmv(R, data, indices, indptr, shape, x)
@@ -178,8 +244,9 @@ def main():
                             shape=np.asarray(shape), B=B, C_base=C_base, C_opt=C_opt)
         index["spmm"][name] = {"nnz": int(data.size), "buckets": meta}
         print("spmm", name, data.size, meta, flush=True)
+    make_coo(index, V, MC)
     index["host"] = host_helper_goldens(R, M)
-    with open(os.path.join(HERE, "index.json"), "w") as f:
+    with open(index_path, "w") as f:
         json.dump(index, f, indent=1, sort_keys=True)
 
 
