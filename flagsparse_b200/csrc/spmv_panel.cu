@@ -101,33 +101,28 @@ __device__ __forceinline__ void ld_words(const uint32_t* piece, int lane, int g,
   }
 }
 
+// The shared-memory state of one CTA: two x buffers, the row accumulators, the two copy barriers.
 template <typename V>
-__global__ void __launch_bounds__(kPanelThreads, 1)
-spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
-                  const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
-                  const V* __restrict__ x, V* __restrict__ y, int64_t n_rows, int64_t n_cols, int rb_rows,
-                  int chunk_cols, int32_t* __restrict__ status) {
-  extern __shared__ __align__(128) unsigned char p_smem[];
-  V* xs = reinterpret_cast<V*>(p_smem);  // 2 * chunk_cols
-  V* y_part = xs + 2 * chunk_cols;       // rb_rows
-  __shared__ __align__(8) uint64_t bars[2];
-  __shared__ int s_failed;
+struct PanelShared {
+  V* xs;      // 2 * chunk_cols
+  V* y_part;  // one accumulator per (virtual) row of the CTA
+  uint64_t* bars;
+  int* failed;
+};
 
+// Units u0 .. u1-1 of one CTA, in order: chunk of x in, pieces added into y_part.  Returns false when a bounded
+// wait ran out (every thread of the CTA gets the same answer).
+template <typename V>
+__device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const uint32_t* __restrict__ rc,
+                                                const int32_t* __restrict__ unit_piece_ptr,
+                                                const int32_t* __restrict__ unit_chunk, int u0, int u1,
+                                                const V* __restrict__ x, int64_t n_cols, int chunk_cols,
+                                                const PanelShared<V>& sh) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rb = blockIdx.x;
-  const int64_t r0 = (int64_t)rb * rb_rows;
-  const int nr = (int)((n_rows - r0) < (int64_t)rb_rows ? (n_rows - r0) : (int64_t)rb_rows);
-  const int u0 = rb_unit_ptr[rb], u1 = rb_unit_ptr[rb + 1];
+  V* xs = sh.xs;
+  V* y_part = sh.y_part;
+  uint64_t* bars = sh.bars;
   const uint32_t col_mask = (uint32_t)(2 * chunk_cols - 1);
-
-  for (int i = tid; i < nr; i += kPanelThreads) y_part[i] = (V)0;
-  if (tid == 0) {
-    s_failed = 0;
-    p_mbar_init(&bars[0], 1);
-    p_mbar_init(&bars[1], 1);
-    p_fence_init();
-  }
-  __syncthreads();
 
   // chunk `c` of x into buffer `b`: bulk copy when the byte count is a multiple of 16, else plain loads
   auto load_chunk = [&](int c, int b) {
@@ -164,7 +159,7 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
       ld_group<G>(val + (size_t)pc * kPieceSlots, lane, 0, v);
       ld_words<G>(rc + (size_t)pc * kPieceSlots, lane, 0, w);
     }
-    if (!p_wait_bounded(&bars[b], (uint32_t)((ord >> 1) & 1))) s_failed = 1;
+    if (!p_wait_bounded(&bars[b], (uint32_t)((ord >> 1) & 1))) *sh.failed = 1;
     if (plain) __syncthreads();
     while (pc < p_end) {
       V acc = (V)0;
@@ -190,13 +185,108 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
       pc += kPanelWarps;
     }
     __syncthreads();  // every add of this unit is done; its x buffer may be refilled
-    if (s_failed) {
-      if (tid == 0 && status != nullptr) atomicExch(status, 2);
-      return;
-    }
+    if (*sh.failed) return false;
     plain = plain_next;
   }
-  for (int i = tid; i < nr; i += kPanelThreads) y[r0 + i] = y_part[i];
+  return true;
+}
+
+template <typename V>
+__device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* smem, uint64_t* bars, int* failed,
+                                            int chunk_cols, int n_acc) {
+  sh.xs = reinterpret_cast<V*>(smem);
+  sh.y_part = sh.xs + 2 * chunk_cols;
+  sh.bars = bars;
+  sh.failed = failed;
+  const int tid = threadIdx.x;
+  for (int i = tid; i < n_acc; i += kPanelThreads) sh.y_part[i] = (V)0;
+  if (tid == 0) {
+    *failed = 0;
+    p_mbar_init(&bars[0], 1);
+    p_mbar_init(&bars[1], 1);
+    p_fence_init();
+  }
+  __syncthreads();
+}
+
+// One CTA per block of rb_rows consecutive rows; every row of y is written exactly once.
+template <typename V>
+__global__ void __launch_bounds__(kPanelThreads, 1)
+spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
+                  const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
+                  const V* __restrict__ x, V* __restrict__ y, int64_t n_rows, int64_t n_cols, int rb_rows,
+                  int chunk_cols, int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char p_smem[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int s_failed;
+  const int tid = threadIdx.x;
+  const int rb = blockIdx.x;
+  const int64_t r0 = (int64_t)rb * rb_rows;
+  const int nr = (int)((n_rows - r0) < (int64_t)rb_rows ? (n_rows - r0) : (int64_t)rb_rows);
+  PanelShared<V> sh;
+  panel_setup<V>(sh, p_smem, bars, &s_failed, chunk_cols, nr);
+  if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x, n_cols,
+                          chunk_cols, sh)) {
+    if (tid == 0 && status != nullptr) atomicExch(status, 2);
+    return;
+  }
+  for (int i = tid; i < nr; i += kPanelThreads) y[r0 + i] = sh.y_part[i];
+}
+
+// Row-group form, for a set of long rows picked out of a matrix (the rest of the matrix goes through the CSR
+// kernels).  The picked rows are numbered q = 0 .. n_long-1 and cut into groups; row q owns the accumulators
+// vbase[q] .. vbase[q+1]-1 of its group ("virtual rows": a row with more than 16 entries in one chunk spreads
+// them over several accumulators, 16 to each, so that the rule "at most 16 entries of an accumulator per
+// unit" still holds).  The units of a group are dealt to several CTAs by column range, so a CTA ends with
+// partial sums of its group's rows: it writes them to part[cta_part_ptr[cta] + (q - first q of the group)],
+// and panel_group_reduce_kernel adds the partial sums of each row in CTA order.
+template <typename V>
+__global__ void __launch_bounds__(kPanelThreads, 1)
+spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc,
+                         const int32_t* __restrict__ unit_piece_ptr, const int32_t* __restrict__ unit_chunk,
+                         const int32_t* __restrict__ cta_unit_ptr, const int32_t* __restrict__ cta_group,
+                         const int32_t* __restrict__ group_q_ptr, const int32_t* __restrict__ vbase,
+                         const int64_t* __restrict__ cta_part_ptr, V* __restrict__ part, const V* __restrict__ x,
+                         int64_t n_cols, int chunk_cols, int32_t* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char p_smem[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int s_failed;
+  const int tid = threadIdx.x;
+  const int cta = blockIdx.x;
+  const int g = cta_group[cta];
+  const int q0 = group_q_ptr[g], q1 = group_q_ptr[g + 1];
+  const int vb0 = vbase[q0];
+  const int n_acc = vbase[q1] - vb0;
+  PanelShared<V> sh;
+  panel_setup<V>(sh, p_smem, bars, &s_failed, chunk_cols, n_acc);
+  if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1], x, n_cols,
+                          chunk_cols, sh)) {
+    if (tid == 0 && status != nullptr) atomicExch(status, 2);
+    return;
+  }
+  V* out = part + cta_part_ptr[cta];
+  for (int i = tid; i < q1 - q0; i += kPanelThreads) {
+    const int a = vbase[q0 + i] - vb0, b = vbase[q0 + i + 1] - vb0;
+    V s = (V)0;
+    for (int v = a; v < b; ++v) s += sh.y_part[v];
+    out[i] = s;
+  }
+}
+
+// y[long_rows[q]] = sum over the CTAs of q's group, in CTA order, of their partial sums (in double).
+template <typename V>
+__global__ void __launch_bounds__(256)
+panel_group_reduce_kernel(const V* __restrict__ part, const int32_t* __restrict__ q_group,
+                          const int32_t* __restrict__ group_q_ptr, const int32_t* __restrict__ group_cta_ptr,
+                          const int64_t* __restrict__ cta_part_ptr, const int32_t* __restrict__ long_rows,
+                          V* __restrict__ y, int n_long) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= n_long) return;
+  const int g = q_group[q];
+  const int i = q - group_q_ptr[g];
+  double s = 0.0;
+  for (int c = group_cta_ptr[g]; c < group_cta_ptr[g + 1]; ++c) s += (double)part[cta_part_ptr[c] + i];
+  y[long_rows[q]] = (V)s;
 }
 
 }  // namespace fsb
@@ -235,6 +325,44 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   } while (0)
   if (vtype == FSB_F32) FSB_PANEL_LAUNCH(float); else FSB_PANEL_LAUNCH(double);
 #undef FSB_PANEL_LAUNCH
+  FSB_RETURN_IF_LAUNCH_FAILED();
+  return FSB_OK;
+}
+
+
+extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                                         const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
+                                         int32_t chunk_cols, int32_t max_group_acc, const int32_t* cta_group,
+                                         const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
+                                         const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
+                                         const int64_t* cta_part_ptr, void* part, const void* x, void* y,
+                                         int64_t n_cols, int32_t* status, void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
+  if (n_cols < 0 || n_ctas < 0 || n_long < 0 || max_group_acc < 0 || max_group_acc >= 65535) return FSB_EINVAL;
+  if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
+  if (n_long == 0 || n_ctas == 0) return FSB_OK;
+  if (!val || !rc || !unit_piece_ptr || !unit_chunk || !cta_unit_ptr || !cta_group || !group_q_ptr ||
+      !group_cta_ptr || !vbase || !q_group || !long_rows || !cta_part_ptr || !part || !x || !y)
+    return FSB_EINVAL;
+  const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols);
+  if (smem > 227 * 1024) return FSB_ERANGE;
+  if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
+  const unsigned rgrid = (unsigned)((n_long + 255) / 256);
+#define FSB_GROUPS_LAUNCH(V)                                                                                       \
+  do {                                                                                                             \
+    cudaError_t e = cudaFuncSetAttribute(spmv_panel_groups_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                               \
+    if (e != cudaSuccess) return cuda_rc(e);                                                                       \
+    spmv_panel_groups_kernel<V><<<(unsigned)n_ctas, kPanelThreads, smem, st>>>(                                    \
+        (const V*)val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr, cta_group, group_q_ptr, vbase, cta_part_ptr,  \
+        (V*)part, (const V*)x, n_cols, chunk_cols, status);                                                        \
+    FSB_RETURN_IF_LAUNCH_FAILED();                                                                                 \
+    panel_group_reduce_kernel<V><<<rgrid, 256, 0, st>>>((const V*)part, q_group, group_q_ptr, group_cta_ptr,       \
+                                                        cta_part_ptr, long_rows, (V*)y, n_long);                   \
+  } while (0)
+  if (vtype == FSB_F32) FSB_GROUPS_LAUNCH(float); else FSB_GROUPS_LAUNCH(double);
+#undef FSB_GROUPS_LAUNCH
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }

@@ -77,6 +77,74 @@ def _cumsum0(counts):
     return out
 
 
+def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, SLOTS, max_slot_overhead):
+    """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of SLOTS slots and
+    lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that follow each
+    other with the same key inside one unit form a run, which must not straddle two pieces and may have at most
+    MAX_RUN entries.  Returns (val, rc, first piece of each unit [n_units + 1], n_pieces), or None when a run is
+    too long or the padding exceeds max_slot_overhead."""
+    dev = data_p.device
+    nnz = data_p.numel()
+    sv = data_p.element_size()
+    ar = torch.arange(nnz, device=dev)
+    new_run = torch.ones(nnz, dtype=torch.bool, device=dev)
+    new_run[1:] = (run_key_p[1:] != run_key_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
+    run_id = torch.cumsum(new_run.to(torch.int64), 0) - 1
+    n_runs = int(run_id[-1].item()) + 1
+    run_first = ar[new_run]                            # global index of each run's first entry
+    run_end = torch.empty(n_runs, dtype=torch.int64, device=dev)
+    run_end[:-1] = run_first[1:]
+    run_end[-1] = nnz
+    max_run = int((run_end - run_first).max().item())
+    del run_end, new_run
+    if max_run > MAX_RUN:
+        return None
+    # Pieces: greedy packing of whole runs into pieces of at most SLOTS entries, all units advancing one
+    # piece per step (the cut after a piece that starts at s is the last run boundary at or before s + SLOTS).
+    n_units = ustart.numel() - 1
+    uend = ustart[1:]
+    cur = ustart[:-1].clone()
+    active = torch.arange(n_units, device=dev)
+    cuts = [cur.clone()]
+    while True:
+        t = cur[active] + SLOTS
+        end_a = uend[active]
+        inside = t < end_a
+        nxt = torch.where(inside, run_first[run_id[torch.clamp(t, max=nnz - 1)]], end_a)
+        cur[active] = nxt
+        keep = nxt < end_a
+        if not bool(keep.any()):
+            break
+        active = active[keep]
+        cuts.append(nxt[keep])
+    piece_start = torch.sort(torch.cat(cuts)).values          # global index of each piece's first entry
+    n_pieces = piece_start.numel()
+    del run_id, run_first, cuts
+    if max_slot_overhead is not None and n_pieces * SLOTS > max_slot_overhead * nnz + 4096:
+        return None
+    piece = torch.searchsorted(piece_start, ar, right=True) - 1
+    slot = ar - piece_start[piece]
+    # inside a piece, slot = 16 * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
+    # contiguous: values at (k // E) * 32 * E + lane * E + k % E (E = values per 16 bytes), words with E = 4
+    lane_, k_ = slot >> 4, slot & 15
+    E = 16 // sv
+    pos_val = piece * SLOTS + (k_ // E) * (32 * E) + lane_ * E + k_ % E
+    pos = piece * SLOTS + (k_ >> 2) * 128 + lane_ * 4 + (k_ & 3)
+    del lane_, k_, slot, piece, ar
+    upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
+    del piece_start
+    field = (u_ord[unit_of_entry] & 1) * CW + (cols_p - (cols_p // CW) * CW)
+    val = torch.zeros(n_pieces * SLOTS, dtype=data_p.dtype, device=dev)
+    val[pos_val] = data_p
+    del pos_val
+    word = (acc_p << 16) | field                         # fits 32 bits: accumulator index < 65535
+    word = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
+    rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)
+    rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
+    rc[pos] = word
+    return val, rc, upiece, n_pieces
+
+
 def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False):
     """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
     nnz = data.numel()
@@ -107,68 +175,15 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     rows_p = rows[perm]
     cols_p = cols[perm]
     del rows, cols, key_sorted
-    ar = torch.arange(nnz, device=dev)
-    j = ar - ustart[unit_of_entry]                     # position inside the unit
-    # runs: maximal groups of consecutive entries of one row inside one unit
-    new_run = torch.ones(nnz, dtype=torch.bool, device=dev)
-    new_run[1:] = (rows_p[1:] != rows_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
-    run_id = torch.cumsum(new_run.to(torch.int64), 0) - 1
-    n_runs = int(run_id[-1].item()) + 1
-    run_first = ar[new_run]                            # global index of each run's first entry
-    run_end = torch.empty(n_runs, dtype=torch.int64, device=dev)
-    run_end[:-1] = run_first[1:]
-    run_end[-1] = nnz
-    max_run = int((run_end - run_first).max().item())
-    del run_end
-    if max_run > MAX_RUN:
-        return None
-    # Pieces: greedy packing of whole runs into pieces of at most SLOTS entries, all units advancing one
-    # piece per step (the cut after a piece that starts at s is the last run boundary at or before s + SLOTS).
-    uend = ustart[1:]
-    cur = ustart[:-1].clone()
-    active = torch.arange(n_units, device=dev)
-    cuts = [cur.clone()]
-    while True:
-        t = cur[active] + SLOTS
-        end_a = uend[active]
-        inside = t < end_a
-        nxt = torch.where(inside, run_first[run_id[torch.clamp(t, max=nnz - 1)]], end_a)
-        cur[active] = nxt
-        keep = nxt < end_a
-        if not bool(keep.any()):
-            break
-        active = active[keep]
-        cuts.append(nxt[keep])
-    piece_start = torch.sort(torch.cat(cuts)).values          # global index of each piece's first entry
-    n_pieces = piece_start.numel()
-    if not force and n_pieces * SLOTS > MAX_SLOT_OVERHEAD * nnz + 4096:
-        return None
-    piece = torch.searchsorted(piece_start, ar, right=True) - 1
-    slot = ar - piece_start[piece]
-    # inside a piece, slot = 16 * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
-    # contiguous: values at (k // E) * 32 * E + lane * E + k % E (E = values per 16 bytes), words with E = 4
-    lane_, k_ = slot >> 4, slot & 15
-    E = 16 // sv
-    pos_val = piece * SLOTS + (k_ // E) * (32 * E) + lane_ * E + k_ % E
-    pos = piece * SLOTS + (k_ >> 2) * 128 + lane_ * 4 + (k_ & 3)
-    del lane_, k_
-    upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
-    del j, run_id, new_run, cuts, piece_start, slot
-    # ordinal of a unit inside its row block decides which of the two x buffers it uses
     rb_unit_ptr = torch.searchsorted(u_rb.contiguous(), torch.arange(n_rb + 1, device=dev))
+    # ordinal of a unit inside its row block decides which of the two x buffers it uses
     u_ord = torch.arange(n_units, device=dev) - rb_unit_ptr[u_rb]
-    rloc = rows_p - (rows_p // RB) * RB
-    field = (u_ord[unit_of_entry] & 1) * CW + (cols_p - (cols_p // CW) * CW)
-    del rows_p, cols_p
-    val = torch.zeros(n_pieces * SLOTS, dtype=data.dtype, device=dev)
-    val[pos_val] = data[perm]
-    del pos_val
-    word = (rloc << 16) | field                         # fits 32 bits: local row < 65535
-    word = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
-    rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)
-    rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
-    rc[pos] = word
-    del pos, perm, rloc, field, unit_of_entry, word
+    packed = pack_pieces(data[perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord, CW,
+                         SLOTS, None if force else MAX_SLOT_OVERHEAD)
+    del rows_p, cols_p, perm, unit_of_entry
+    if packed is None:
+        return None
+    val, rc, upiece, n_pieces = packed
 
     lay = PanelLayout()
     lay.val, lay.rc = val, rc

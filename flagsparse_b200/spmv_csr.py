@@ -35,6 +35,12 @@ _UNIFORM_ROW_SLACK = 64
 # regroup banded matrices for the panel kernel (costs a second copy of the entries); FSB_SPMV_PANEL=0 turns it off
 _PANEL_ENABLED = os.environ.get("FSB_SPMV_PANEL", "1") != "0"
 
+
+def _long_rows_enabled():
+    """Split the long rows of skewed matrices off to the row-group panel kernel; FSB_SPMV_LONG_ROWS=0 turns it off."""
+    return os.environ.get("FSB_SPMV_LONG_ROWS", "1") != "0"
+
+
 _ALGO_NAMES = {"auto": _lib.FSB_SPMV_AUTO, "vector": _lib.FSB_SPMV_VECTOR, "stream": _lib.FSB_SPMV_STREAM,
                "panel": _lib.FSB_SPMV_PANEL}
 
@@ -82,11 +88,12 @@ class PreparedCsrSpmv:
     __slots__ = (
         "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "block_nnz",
         "max_segments", "max_row_nnz", "opt_buckets", "supports_opt", "stats", "algo", "tuning",
-        "tile_nnz", "tile_row", "scratch", "panel",
+        "tile_nnz", "tile_row", "scratch", "panel", "long_rows",
     )
 
     def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
-                 max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch, panel=None):
+                 max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch, panel=None,
+                 long_rows=None):
         self.data = data
         self.kernel_indices = kernel_indices
         self.kernel_indptr = kernel_indptr
@@ -104,8 +111,11 @@ class PreparedCsrSpmv:
         self.tile_row = tile_row
         self.scratch = scratch
         self.panel = panel
+        self.long_rows = long_rows   # (prepared short-row part, LongRowLayout) when the long rows were split off
         n_tiles = 0 if tile_row is None else tile_row.numel() - 1
         kind = {_lib.FSB_SPMV_STREAM: "stream", _lib.FSB_SPMV_PANEL: "panel"}.get(algo, "vector")
+        if long_rows is not None:
+            kind = "long-row panel + " + long_rows[0].opt_buckets[0]["kind"]
         self.opt_buckets = [{"kind": kind, "tile_nnz": tile_nnz, "n_tiles": n_tiles, "n_rows": n_rows}]
 
 
@@ -176,7 +186,28 @@ def prepare_spmv_csr(data, indices, indptr, shape, block_nnz=256, max_segments=N
     return _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected=True)
 
 
-def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected):
+def _split_long_rows(data, kernel_indices, kernel_indptr, n_rows, n_cols, shape, block_nnz, max_segments):
+    """(prepared short-row part, LongRowLayout) for a skewed matrix whose long rows hold a large share of the
+    entries, else None."""
+    from . import longrows
+
+    nnz = data.numel()
+    threshold = longrows.long_row_threshold()
+    lens, candidates, cand_nnz = longrows.split_rows(kernel_indptr, n_rows, threshold or longrows.MIN_CANDIDATE_LEN)
+    enough = lambda k: k >= longrows.MIN_LONG_NNZ and k >= longrows.MIN_LONG_SHARE * nnz  # noqa: E731
+    if not enough(cand_nnz):
+        return None
+    built = longrows.build_long_row_layout(data, kernel_indices, kernel_indptr, lens, candidates, n_cols,
+                                           min_unit_entries=0 if threshold else longrows.MIN_UNIT_ENTRIES)
+    if built is None or not enough(built[0].nnz):
+        return None
+    layout, is_long = built
+    d_s, i_s, p_s = longrows.short_part(data, kernel_indices, kernel_indptr, lens, is_long)
+    short = _prepare_spmv_csr(d_s, i_s, p_s, shape, block_nnz, max_segments, reuse_expected=True, allow_split=False)
+    return short, layout
+
+
+def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reuse_expected, allow_split=True):
     """reuse_expected=False (a one-shot product) skips the panel regrouping, which costs about as much as a
     hundred products and only pays when the prepared matrix is used again."""
     data, kernel_indices, kernel_indptr, n_rows, n_cols, stats = _prepare_spmv_csr_matrix(
@@ -205,11 +236,17 @@ def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reu
         tile_row = _tile_plan(kernel_indptr, n_rows, nnz, tile_nnz)
         scratch = torch.empty(int(L.fsb_spmv_csr_scratch_bytes(vt, nnz, tuning)), dtype=torch.uint8,
                               device=data.device)
+    # skewed rows: the long ones leave for the row-group panel kernel, the CSR kernels keep the short ones
+    long_rows = None
+    if (algo == _lib.FSB_SPMV_STREAM and allow_split and reuse_expected and _long_rows_enabled()
+            and os.environ.get("FSB_SPMV_ALGO", "") == ""):
+        long_rows = _split_long_rows(data, kernel_indices, kernel_indptr, n_rows, n_cols, shape, block_nnz,
+                                     max_segments)
     return PreparedCsrSpmv(
         data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape, n_rows=n_rows,
         n_cols=n_cols, block_nnz=block_nnz_use, max_segments=max_segments_use, max_row_nnz=max_row_nnz,
         stats=stats, algo=algo, tuning=tuning, tile_nnz=tile_nnz, tile_row=tile_row, scratch=scratch,
-        panel=panel_layout,
+        panel=panel_layout, long_rows=long_rows,
     )
 
 
@@ -225,6 +262,14 @@ def _spmv_launch(prepared, x, y):
 
         with torch.cuda.device(dev):
             panel.launch_panel(p.panel, x, y, p.n_rows, p.n_cols, _stream_ptr(dev))
+        return
+    if p.long_rows is not None:
+        from . import longrows
+
+        short, layout = p.long_rows
+        _spmv_launch(short, x, y)      # every row of y; the long rows get zeros here
+        with torch.cuda.device(dev):
+            longrows.launch_long_rows(layout, x, y, p.n_cols, _stream_ptr(dev))
         return
     algo = p.algo if p.tile_row is not None else _lib.FSB_SPMV_VECTOR
     tuning = p.tuning if algo == _lib.FSB_SPMV_STREAM else (p.tuning & 0xFF if p.tuning & 0xFF in (2, 4, 8, 16, 32) else 0)

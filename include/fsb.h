@@ -144,6 +144,32 @@ int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int
                        int64_t n_cols, int32_t* status, void* stream);
 
 /*
+ * Row-group form of the panel product, for the LONG rows of a skewed matrix: y[long_rows[q]] = (A x)[long_rows[q]]
+ * for q = 0 .. n_long-1; the other rows of y are not touched (the host code runs fsb_spmv_csr on the remaining
+ * short rows first).  Replaces, for those rows, the long-row buckets of _triton_spmv_csr_impl_opt_prepared
+ * (spmv_csr.py:329-376 with the bucket tables :64-89: one Triton program per long row).
+ * The picked rows are cut into groups; row q owns accumulators vbase[q] .. vbase[q+1]-1 ("virtual rows": at most
+ * 16 entries of a virtual row in one column chunk) and the packed word of a slot holds the virtual row relative
+ * to its group.  The units (group x column chunk) are ordered by group, then chunk, and dealt to n_ctas CTAs:
+ *   cta_unit_ptr         units [cta_unit_ptr[c], cta_unit_ptr[c+1]) belong to CTA c (parity of a slot's packed
+ *                        word = ordinal of the unit inside its CTA modulo 2)
+ *   cta_group            group of CTA c;  group_cta_ptr: CTAs [group_cta_ptr[g], group_cta_ptr[g+1]) work on group g
+ *   group_q_ptr          rows q in [group_q_ptr[g], group_q_ptr[g+1]) form group g;  q_group[q]: group of row q
+ *   max_group_acc        largest number of accumulators of a group (shared memory: fsb_spmv_panel_smem_bytes)
+ *   cta_part_ptr, part   CTA c writes one partial sum per row of its group to part[cta_part_ptr[c] + ...]; a
+ *                        second kernel adds the partial sums of a row in CTA order (in double) and stores y.
+ *                        part must hold sum over CTAs of the row count of their group, in elements of vtype.
+ * Everything else as for fsb_spmv_csr_panel.  Results are bit-reproducible.
+ */
+int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                              const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
+                              int32_t chunk_cols, int32_t max_group_acc, const int32_t* cta_group,
+                              const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
+                              const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
+                              const int64_t* cta_part_ptr, void* part, const void* x, void* y, int64_t n_cols,
+                              int32_t* status, void* stream);
+
+/*
  * y = A x with the STREAM algorithm for callers that must not (or cannot) allocate device memory: code
  * running inside a frozen or fixed-size memory pool, plugins that only ever receive buffers from their
  * host framework, latency-critical loops where cudaMalloc's device-wide synchronisation is unacceptable.
