@@ -383,6 +383,14 @@ def run_ours(args, workload):
             step = lambda: fs.flagsparse_spmv_csr(x=x, prepared=prep, out=out)  # noqa: E731
             nnz = d.numel()
             launches_per_step = 2 if prep.algo == _lib.FSB_SPMV_STREAM else 1
+            if prep.long_rows is not None:
+                # short rows (stream kernel + fix-up, or one vector kernel), then the long-row panel kernel + its reduction
+                short, lay = prep.long_rows
+                launches_per_step = (2 if short.algo == _lib.FSB_SPMV_STREAM and short.tile_row is not None else 1) + 2
+                extra["long_rows"] = {"rows": lay.n_long, "nnz": lay.nnz, "groups": lay.n_groups, "ctas": lay.n_ctas,
+                                      "units": lay.n_units, "x_overhead": round(lay.x_overhead, 3),
+                                      "slot_overhead": round(lay.slot_overhead, 3), "layout_bytes": lay.nbytes(),
+                                      "short_nnz": short.data.numel()}
             si, sp_ = prep.kernel_indices.element_size(), prep.kernel_indptr.element_size()
             extra["kernel"] = prep.opt_buckets[0]["kind"]
             if prep.panel is not None:

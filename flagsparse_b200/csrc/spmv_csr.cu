@@ -248,8 +248,17 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
       const bool is_huge = e - s > HUGE_LEN;
       const bool is_long = is_huge || ((L < 32) && (e - s > long_len));
       V acc = 0;
-      if (!is_long)
-        for (int p = s + lane; p < e; p += L) acc += s_prod[p];
+      if (!is_long) {
+        // four independent partial sums: four shared-memory loads in flight instead of a chain of single ones
+        V a1 = 0, a2 = 0, a3 = 0;
+        for (int p = s + lane; p < e; p += 4 * L) {
+          acc += s_prod[p];
+          if (p + L < e) a1 += s_prod[p + L];
+          if (p + 2 * L < e) a2 += s_prod[p + 2 * L];
+          if (p + 3 * L < e) a3 += s_prod[p + 3 * L];
+        }
+        acc = (acc + a1) + (a2 + a3);
+      }
       for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
       if (valid && lane == 0) {
         if (is_huge) {

@@ -75,11 +75,6 @@ class ShardedCsrSpmv:
         self.row_ranges = [(int(s), int(n)) for s, n in ranges]
         self._check_cover()
         self._local_spmv = local_spmv
-        self.prepared = None
-        if local_spmv is None:
-            from .spmv_csr import prepare_spmv_csr
-
-            self.prepared = prepare_spmv_csr(data, indices, indptr, (self.n_local, self.n_cols))
         if mode == "auto":
             # the fused exchange needs the CUDA kernels, several ranks and something to multiply
             fused_ok = local_spmv is None and self.world > 1 and data.is_cuda
@@ -88,6 +83,13 @@ class ShardedCsrSpmv:
             raise ValueError("mode must be 'auto', 'nccl' or 'peer'")
         if mode == "peer" and local_spmv is not None:
             raise ValueError("mode 'peer' fuses the exchange into the CUDA kernel; it cannot take local_spmv")
+        self.prepared = None
+        if local_spmv is None:
+            from .spmv_csr import _prepare_spmv_csr
+
+            # the peer-store epilogue exists for the vector and the stream kernel only: no regrouped layouts there
+            self.prepared = _prepare_spmv_csr(data, indices, indptr, (self.n_local, self.n_cols), 256, None,
+                                              reuse_expected=mode != "peer")
         self.mode = mode
         self._y = None
         self._symm = None
