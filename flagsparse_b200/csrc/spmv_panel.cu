@@ -62,12 +62,17 @@ __device__ __forceinline__ bool p_wait_bounded(uint64_t* bar, uint32_t phase) {
 template <typename V, int G>
 __device__ __forceinline__ void panel_rounds(const V (&v)[G], const uint32_t (&w)[G], uint32_t next_word, V& acc,
                                              const V* __restrict__ xs, V* __restrict__ y_part, uint32_t col_mask) {
+  // x does not change during a unit: all G gathers go out first, so that their latencies overlap instead of
+  // queueing behind the per-round ordering points below
+  V p[G];
+#pragma unroll
+  for (int k = 0; k < G; ++k) p[k] = v[k] * xs[w[k] & col_mask];   // padding slots: value 0, column 0
 #pragma unroll
   for (int k = 0; k < G; ++k) {
     const uint32_t row = w[k] >> 16;
     const uint32_t next_row = (k + 1 < G ? w[k + 1] : next_word) >> 16;
     const bool live = row != kNoRow;
-    if (live) acc += v[k] * xs[w[k] & col_mask];
+    if (live) acc += p[k];
     if (live && next_row != row) {
       y_part[row] += acc;
       acc = (V)0;
@@ -101,28 +106,42 @@ __device__ __forceinline__ void ld_words(const uint32_t* piece, int lane, int g,
   }
 }
 
-// The shared-memory state of one CTA: two x buffers, the row accumulators, the two copy barriers.
+constexpr int kMaxXBuffers = 8;
+constexpr int kUnitWindow = 512;   // units whose tables are kept in shared memory at a time
+constexpr int kUnitLookahead = kMaxXBuffers;
+
+// The shared-memory state of one CTA: the x buffers, the row accumulators, the copy barriers, the unit tables.
 template <typename V>
 struct PanelShared {
-  V* xs;      // 2 * chunk_cols
+  V* xs;      // n_buf * chunk_cols
   V* y_part;  // one accumulator per (virtual) row of the CTA
   uint64_t* bars;
   int* failed;
+  int32_t* upp;   // unit_piece_ptr of the current window of units (kUnitWindow + 1 entries)
+  int32_t* uch;   // unit_chunk of the window and of the next few units (kUnitWindow + kUnitLookahead)
 };
 
 // Units u0 .. u1-1 of one CTA, in order: chunk of x in, pieces added into y_part.  Returns false when a bounded
 // wait ran out (every thread of the CTA gets the same answer).
+//   - x chunks are fetched n_buf - 1 units ahead into n_buf buffers (unit number `ord` of the CTA uses buffer
+//     ord % n_buf; the packed word of a slot already holds buffer * chunk_cols + local column);
+//   - the pieces of the CTA are dealt to its warps round-robin ACROSS units (piece p goes to warp
+//     (p - first piece of the CTA) % 32), and a warp fetches the first entries of its next piece while it works
+//     on the current one, whichever unit that piece belongs to: a unit with only a few pieces costs neither a
+//     trip to DRAM for its entries nor one for its tables.
 template <typename V>
 __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const uint32_t* __restrict__ rc,
                                                 const int32_t* __restrict__ unit_piece_ptr,
                                                 const int32_t* __restrict__ unit_chunk, int u0, int u1,
-                                                const V* __restrict__ x, int64_t n_cols, int chunk_cols,
+                                                const V* __restrict__ x, int64_t n_cols, int chunk_cols, int n_buf,
                                                 const PanelShared<V>& sh) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   V* xs = sh.xs;
   V* y_part = sh.y_part;
   uint64_t* bars = sh.bars;
-  const uint32_t col_mask = (uint32_t)(2 * chunk_cols - 1);
+  const uint32_t col_mask = (uint32_t)(n_buf * chunk_cols - 1);
+  const int buf_mask = n_buf - 1;
+  if (u0 >= u1) return true;
 
   // chunk `c` of x into buffer `b`: bulk copy when the byte count is a multiple of 16, else plain loads
   auto load_chunk = [&](int c, int b) {
@@ -141,96 +160,122 @@ __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const
     return true;
   };
 
-  bool plain = false;  // some chunk of this unit was written with ordinary stores: needs a CTA barrier
-  if (u0 < u1) plain = load_chunk(unit_chunk[u0], 0);
-  for (int u = u0; u < u1; ++u) {
-    const int ord = u - u0, b = ord & 1;
-    // the other buffer was last read before the barrier that closed the previous unit: free to refill
-    bool plain_next = false;
-    if (u + 1 < u1) plain_next = load_chunk(unit_chunk[u + 1], b ^ 1);
-    const int p_end = unit_piece_ptr[u + 1];
-    int pc = unit_piece_ptr[u] + warp;
-    constexpr int G = sizeof(V) == 4 ? 8 : 4;   // slots per load group
-    constexpr int NG = kPieceRounds / G;        // groups per piece
-    // the entries do not depend on x: start fetching the first group before waiting for the chunk
-    V v[G];
-    uint32_t w[G];
-    if (pc < p_end) {
-      ld_group<G>(val + (size_t)pc * kPieceSlots, lane, 0, v);
-      ld_words<G>(rc + (size_t)pc * kPieceSlots, lane, 0, w);
-    }
-    if (!p_wait_bounded(&bars[b], (uint32_t)((ord >> 1) & 1))) *sh.failed = 1;
-    if (plain) __syncthreads();
-    while (pc < p_end) {
-      V acc = (V)0;
+  constexpr int G = sizeof(V) == 4 ? 8 : 4;   // slots per load group
+  constexpr int NG = kPieceRounds / G;        // groups per piece
+  const int p_cta_end = unit_piece_ptr[u1];
+  int pc = unit_piece_ptr[u0] + warp;         // this warp's next piece
+  // the entries do not depend on x: the first group of the warp's first piece is fetched before anything else
+  V v[G];
+  uint32_t w[G];
+  if (pc < p_cta_end) {
+    ld_group<G>(val + (size_t)pc * kPieceSlots, lane, 0, v);
+    ld_words<G>(rc + (size_t)pc * kPieceSlots, lane, 0, w);
+  }
+  // chunks of the first n_buf - 1 units
+  bool plain = false;  // some chunk was written with ordinary stores: needs a CTA barrier before its first use
+  for (int a = 0; a < n_buf - 1 && u0 + a < u1; ++a) plain |= load_chunk(unit_chunk[u0 + a], a);
+
+  for (int w0 = u0; w0 < u1; w0 += kUnitWindow) {
+    const int nwin = (u1 - w0) < kUnitWindow ? (u1 - w0) : kUnitWindow;
+    const int nch = (u1 - w0) < (kUnitWindow + kUnitLookahead) ? (u1 - w0) : (kUnitWindow + kUnitLookahead);
+    if (w0 > u0) __syncthreads();  // the previous window's tables are no longer read
+    for (int i = tid; i <= nwin; i += kPanelThreads) sh.upp[i] = unit_piece_ptr[w0 + i];
+    for (int i = tid; i < nch; i += kPanelThreads) sh.uch[i] = unit_chunk[w0 + i];
+    __syncthreads();
+    for (int u = w0; u < w0 + nwin; ++u) {
+      const int ord = u - u0, b = ord & buf_mask;
+      // the buffer of the previous unit was last read before the barrier that closed it: free to refill
+      if (u + n_buf - 1 < u1) plain |= load_chunk(sh.uch[u + n_buf - 1 - w0], (ord + n_buf - 1) & buf_mask);
+      const int p_end = sh.upp[u - w0 + 1];
+      if (!p_wait_bounded(&bars[b], (uint32_t)((ord / n_buf) & 1))) *sh.failed = 1;
+      if (plain && ord == 0) __syncthreads();  // later plain chunks are written at least one unit (barrier) ahead
+      while (pc < p_end) {
+        V acc = (V)0;
 #pragma unroll
-      for (int g = 0; g < NG; ++g) {
-        // next group (of this piece, or the first one of this warp's next piece) in flight while this one is used
-        V v2[G];
-        uint32_t w2[G];
-        const bool more = g + 1 < NG;
-        const int np = more ? pc : pc + kPanelWarps;
-        const bool have = np < p_end;
-        if (have) {
-          ld_group<G>(val + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, v2);
-          ld_words<G>(rc + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, w2);
-        }
-        const uint32_t next_word = more ? w2[0] : (kNoRow << 16);  // a lane's run ends with its last slot
-        panel_rounds<V, G>(v, w, next_word, acc, xs, y_part, col_mask);
-        if (have) {
+        for (int g = 0; g < NG; ++g) {
+          // next group (of this piece, or the first one of this warp's next piece) in flight while this one is used
+          V v2[G];
+          uint32_t w2[G];
+          const bool more = g + 1 < NG;
+          const int np = more ? pc : pc + kPanelWarps;
+          const bool have = np < p_cta_end;
+          if (have) {
+            ld_group<G>(val + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, v2);
+            ld_words<G>(rc + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, w2);
+          }
+          const uint32_t next_word = more ? w2[0] : (kNoRow << 16);  // a lane's run ends with its last slot
+          panel_rounds<V, G>(v, w, next_word, acc, xs, y_part, col_mask);
+          if (have) {
 #pragma unroll
-          for (int k = 0; k < G; ++k) { v[k] = v2[k]; w[k] = w2[k]; }
+            for (int k = 0; k < G; ++k) { v[k] = v2[k]; w[k] = w2[k]; }
+          }
         }
+        pc += kPanelWarps;
       }
-      pc += kPanelWarps;
+      __syncthreads();  // every add of this unit is done; its x buffer may be refilled
+      if (*sh.failed) return false;
     }
-    __syncthreads();  // every add of this unit is done; its x buffer may be refilled
-    if (*sh.failed) return false;
-    plain = plain_next;
   }
   return true;
 }
 
+struct PanelStatic {
+  uint64_t bars[kMaxXBuffers];
+  int32_t upp[kUnitWindow + 1];
+  int32_t uch[kUnitWindow + kUnitLookahead];
+  int failed;
+};
+
 template <typename V>
-__device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* smem, uint64_t* bars, int* failed,
-                                            int chunk_cols, int n_acc) {
+__device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* smem, PanelStatic* st, int chunk_cols,
+                                            int n_buf, int n_acc) {
   sh.xs = reinterpret_cast<V*>(smem);
-  sh.y_part = sh.xs + 2 * chunk_cols;
-  sh.bars = bars;
-  sh.failed = failed;
+  sh.y_part = sh.xs + (size_t)n_buf * chunk_cols;
+  sh.bars = st->bars;
+  sh.failed = &st->failed;
+  sh.upp = st->upp;
+  sh.uch = st->uch;
   const int tid = threadIdx.x;
   for (int i = tid; i < n_acc; i += kPanelThreads) sh.y_part[i] = (V)0;
   if (tid == 0) {
-    *failed = 0;
-    p_mbar_init(&bars[0], 1);
-    p_mbar_init(&bars[1], 1);
+    st->failed = 0;
+    for (int b = 0; b < n_buf; ++b) p_mbar_init(&st->bars[b], 1);
     p_fence_init();
   }
   __syncthreads();
 }
 
-// One CTA per block of rb_rows consecutive rows; every row of y is written exactly once.
+// One CTA per block of rb_rows consecutive rows; every row of y is written exactly once (to y, or, when y_peers
+// is given, to y_peers[p][row_offset + row] for every p).
 template <typename V>
 __global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
                   const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
-                  const V* __restrict__ x, V* __restrict__ y, int64_t n_rows, int64_t n_cols, int rb_rows,
-                  int chunk_cols, int32_t* __restrict__ status) {
+                  const V* __restrict__ x, V* __restrict__ y, V* const* __restrict__ y_peers, int n_peers,
+                  int64_t row_offset, int64_t n_rows, int64_t n_cols, int rb_rows, int chunk_cols, int n_buf,
+                  int32_t* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char p_smem[];
-  __shared__ __align__(8) uint64_t bars[2];
-  __shared__ int s_failed;
+  __shared__ __align__(8) PanelStatic p_static;
   const int tid = threadIdx.x;
   const int rb = blockIdx.x;
   const int64_t r0 = (int64_t)rb * rb_rows;
   const int nr = (int)((n_rows - r0) < (int64_t)rb_rows ? (n_rows - r0) : (int64_t)rb_rows);
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, bars, &s_failed, chunk_cols, nr);
+  panel_setup<V>(sh, p_smem, &p_static, chunk_cols, n_buf, nr);
   if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x, n_cols,
-                          chunk_cols, sh)) {
+                          chunk_cols, n_buf, sh)) {
     if (tid == 0 && status != nullptr) atomicExch(status, 2);
     return;
   }
-  for (int i = tid; i < nr; i += kPanelThreads) y[r0 + i] = sh.y_part[i];
+  if (y_peers == nullptr) {
+    for (int i = tid; i < nr; i += kPanelThreads) y[r0 + i] = sh.y_part[i];
+  } else {
+    // sharded product: this GPU's rows go straight into every GPU's copy of y (coalesced stores over NVLink)
+    for (int p = 0; p < n_peers; ++p) {
+      V* dst = y_peers[p] + row_offset + r0;
+      for (int i = tid; i < nr; i += kPanelThreads) dst[i] = sh.y_part[i];
+    }
+  }
 }
 
 // Row-group form, for a set of long rows picked out of a matrix (the rest of the matrix goes through the CSR
@@ -247,10 +292,9 @@ spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__
                          const int32_t* __restrict__ cta_unit_ptr, const int32_t* __restrict__ cta_group,
                          const int32_t* __restrict__ group_q_ptr, const int32_t* __restrict__ vbase,
                          const int64_t* __restrict__ cta_part_ptr, V* __restrict__ part, const V* __restrict__ x,
-                         int64_t n_cols, int chunk_cols, int32_t* __restrict__ status) {
+                         int64_t n_cols, int chunk_cols, int n_buf, int32_t* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char p_smem[];
-  __shared__ __align__(8) uint64_t bars[2];
-  __shared__ int s_failed;
+  __shared__ __align__(8) PanelStatic p_static;
   const int tid = threadIdx.x;
   const int cta = blockIdx.x;
   const int g = cta_group[cta];
@@ -258,9 +302,9 @@ spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__
   const int vb0 = vbase[q0];
   const int n_acc = vbase[q1] - vb0;
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, bars, &s_failed, chunk_cols, n_acc);
+  panel_setup<V>(sh, p_smem, &p_static, chunk_cols, n_buf, n_acc);
   if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1], x, n_cols,
-                          chunk_cols, sh)) {
+                          chunk_cols, n_buf, sh)) {
     if (tid == 0 && status != nullptr) atomicExch(status, 2);
     return;
   }
@@ -295,24 +339,32 @@ using namespace fsb;
 
 extern "C" int fsb_spmv_panel_piece_slots(void) { return kPieceSlots; }
 
-extern "C" size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols) {
+extern "C" size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers) {
   const size_t sv = vtype == FSB_F32 ? 4 : 8;
-  return 2 * (size_t)chunk_cols * sv + (((size_t)rb_rows + 3) & ~(size_t)3) * sv;
+  return (size_t)n_buffers * (size_t)chunk_cols * sv + (((size_t)rb_rows + 3) & ~(size_t)3) * sv;
 }
 
-extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
-                                  const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
-                                  int32_t rb_rows, int32_t chunk_cols, const void* x, void* y, int64_t n_rows,
-                                  int64_t n_cols, int32_t* status, void* stream_) {
+extern "C" size_t fsb_spmv_panel_static_smem_bytes(void) { return sizeof(PanelStatic); }
+
+static bool panel_buffers_ok(int n_buffers, int chunk_cols) {
+  return (n_buffers == 2 || n_buffers == 4 || n_buffers == 8) && (int64_t)n_buffers * chunk_cols <= 65536;
+}
+
+static int panel_launch(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                        const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks, int32_t rb_rows,
+                        int32_t chunk_cols, int32_t n_buffers, const void* x, void* y, void* const* y_peers,
+                        int n_peers, int64_t row_offset, int64_t n_rows, int64_t n_cols, int32_t* status,
+                        void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
   if (n_rows < 0 || n_cols < 0 || n_row_blocks < 0 || rb_rows <= 0 || rb_rows >= 65535) return FSB_EINVAL;
   if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
+  if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
   if (n_rows == 0) return FSB_OK;
   if ((int64_t)n_row_blocks * rb_rows < n_rows) return FSB_EINVAL;
-  if (!val || !rc || !unit_piece_ptr || !unit_chunk || !rb_unit_ptr || !x || !y) return FSB_EINVAL;
-  const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols);
-  if (smem > 227 * 1024) return FSB_ERANGE;
+  if (!val || !rc || !unit_piece_ptr || !unit_chunk || !rb_unit_ptr || !x || (!y && !y_peers)) return FSB_EINVAL;
+  const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols, n_buffers);
+  if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
 #define FSB_PANEL_LAUNCH(V)                                                                                   \
   do {                                                                                                        \
@@ -320,8 +372,8 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
                                          (int)smem);                                                          \
     if (e != cudaSuccess) return cuda_rc(e);                                                                  \
     spmv_panel_kernel<V><<<(unsigned)n_row_blocks, kPanelThreads, smem, st>>>(                                \
-        (const V*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const V*)x, (V*)y, n_rows, n_cols,       \
-        rb_rows, chunk_cols, status);                                                                         \
+        (const V*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const V*)x, (V*)y, (V* const*)y_peers,   \
+        n_peers, row_offset, n_rows, n_cols, rb_rows, chunk_cols, n_buffers, status);                         \
   } while (0)
   if (vtype == FSB_F32) FSB_PANEL_LAUNCH(float); else FSB_PANEL_LAUNCH(double);
 #undef FSB_PANEL_LAUNCH
@@ -329,10 +381,30 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   return FSB_OK;
 }
 
+extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                                  const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
+                                  int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x, void* y,
+                                  int64_t n_rows, int64_t n_cols, int32_t* status, void* stream_) {
+  if (y == nullptr && n_rows > 0) return FSB_EINVAL;
+  return panel_launch(vtype, val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, n_row_blocks, rb_rows, chunk_cols,
+                      n_buffers, x, y, nullptr, 0, 0, n_rows, n_cols, status, stream_);
+}
+
+extern "C" int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc,
+                                          const int32_t* unit_piece_ptr, const int32_t* unit_chunk,
+                                          const int32_t* rb_unit_ptr, int32_t n_row_blocks, int32_t rb_rows,
+                                          int32_t chunk_cols, int32_t n_buffers, const void* x, void* const* y_peers,
+                                          int n_peers, int64_t row_offset, int64_t n_rows, int64_t n_cols,
+                                          int32_t* status, void* stream_) {
+  if (y_peers == nullptr || n_peers < 1 || n_peers > 64 || row_offset < 0) return FSB_EINVAL;
+  return panel_launch(vtype, val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, n_row_blocks, rb_rows, chunk_cols,
+                      n_buffers, x, nullptr, y_peers, n_peers, row_offset, n_rows, n_cols, status, stream_);
+}
 
 extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                                          const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
-                                         int32_t chunk_cols, int32_t max_group_acc, const int32_t* cta_group,
+                                         int32_t chunk_cols, int32_t n_buffers, int32_t max_group_acc,
+                                         const int32_t* cta_group,
                                          const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
                                          const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
                                          const int64_t* cta_part_ptr, void* part, const void* x, void* y,
@@ -341,12 +413,13 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
   if (n_cols < 0 || n_ctas < 0 || n_long < 0 || max_group_acc < 0 || max_group_acc >= 65535) return FSB_EINVAL;
   if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
+  if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
   if (n_long == 0 || n_ctas == 0) return FSB_OK;
   if (!val || !rc || !unit_piece_ptr || !unit_chunk || !cta_unit_ptr || !cta_group || !group_q_ptr ||
       !group_cta_ptr || !vbase || !q_group || !long_rows || !cta_part_ptr || !part || !x || !y)
     return FSB_EINVAL;
-  const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols);
-  if (smem > 227 * 1024) return FSB_ERANGE;
+  const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols, n_buffers);
+  if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
   const unsigned rgrid = (unsigned)((n_long + 255) / 256);
 #define FSB_GROUPS_LAUNCH(V)                                                                                       \
@@ -356,7 +429,7 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
     if (e != cudaSuccess) return cuda_rc(e);                                                                       \
     spmv_panel_groups_kernel<V><<<(unsigned)n_ctas, kPanelThreads, smem, st>>>(                                    \
         (const V*)val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr, cta_group, group_q_ptr, vbase, cta_part_ptr,  \
-        (V*)part, (const V*)x, n_cols, chunk_cols, status);                                                        \
+        (V*)part, (const V*)x, n_cols, chunk_cols, n_buffers, status);                                             \
     FSB_RETURN_IF_LAUNCH_FAILED();                                                                                 \
     panel_group_reduce_kernel<V><<<rgrid, 256, 0, st>>>((const V*)part, q_group, group_q_ptr, group_cta_ptr,       \
                                                         cta_part_ptr, long_rows, (V*)y, n_long);                   \

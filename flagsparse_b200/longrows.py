@@ -39,7 +39,7 @@ ACC_CAP = None              # accumulators per group; None = what fits in shared
 class LongRowLayout:
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "cta_unit_ptr", "cta_group", "group_q_ptr",
                  "group_cta_ptr", "vbase", "q_group", "long_rows", "cta_part_ptr", "part", "n_ctas", "n_groups",
-                 "n_long", "chunk_cols", "max_group_acc", "n_units", "n_pieces", "nnz", "x_overhead",
+                 "n_long", "chunk_cols", "n_buffers", "max_group_acc", "n_units", "n_pieces", "nnz", "x_overhead",
                  "slot_overhead", "status")
 
     def nbytes(self):
@@ -48,12 +48,11 @@ class LongRowLayout:
         return sum(getattr(self, n).numel() * getattr(self, n).element_size() for n in names)
 
 
-def _accumulator_cap(dtype, chunk_cols):
+def _accumulator_cap(dtype, chunk_cols, n_buffers):
     L = _lib.lib()
     sv = 4 if dtype == torch.float32 else 8
-    budget = 222 * 1024 - 1024
-    fixed = int(L.fsb_spmv_panel_smem_bytes(_VTYPE[dtype], 0, chunk_cols))
-    return min(49152, (budget - fixed) // sv // 64 * 64)
+    fixed = int(L.fsb_spmv_panel_smem_bytes(_VTYPE[dtype], 0, chunk_cols, n_buffers))
+    return min(49152, (_panel.smem_budget() - fixed) // sv // 64 * 64)
 
 
 def long_row_threshold():
@@ -87,7 +86,8 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     sv = data.element_size()
     CW = chunk_cols or int(os.environ.get("FSB_PANEL_CHUNK", "0")) or (8192 if sv == 4 else 4096)
     SLOTS = int(_lib.lib().fsb_spmv_panel_piece_slots())
-    cap = acc_cap or ACC_CAP or _accumulator_cap(data.dtype, CW)
+    NB = _panel.default_buffers()
+    cap = acc_cap or ACC_CAP or _accumulator_cap(data.dtype, CW, NB)
     if n_ctas_target is None:
         try:
             n_ctas_target = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -189,7 +189,7 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     acc_p = vrow_p - group_vb[q_group[q_p]]
     del q_p, sub_p
     packed = _panel.pack_pieces(data[src[perm]], acc_p, cols[perm], vrow_p, unit_of_entry, ustart, u_ord, CW, SLOTS,
-                                None)
+                                None, n_buffers=NB)
     del acc_p, vrow_p, unit_of_entry, src, cols, perm
     if packed is None:
         return None
@@ -205,7 +205,7 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     lay.cta_part_ptr = cta_part_ptr[:-1].contiguous()
     lay.part = torch.zeros(max(1, int(cta_part_ptr[-1].item())), dtype=data.dtype, device=dev)
     lay.n_ctas, lay.n_groups, lay.n_long = n_ctas, n_groups, n_long
-    lay.chunk_cols, lay.max_group_acc = CW, max_group_acc
+    lay.chunk_cols, lay.n_buffers, lay.max_group_acc = CW, NB, max_group_acc
     lay.n_units, lay.n_pieces, lay.nnz = n_units, n_pieces, nnz
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)
@@ -220,7 +220,7 @@ def launch_long_rows(layout, x, y, n_cols, stream_ptr):
     la = layout
     rc = _lib.lib().fsb_spmv_csr_panel_groups(
         _VTYPE[la.val.dtype], la.val.data_ptr(), la.rc.data_ptr(), la.unit_piece_ptr.data_ptr(),
-        la.unit_chunk.data_ptr(), la.cta_unit_ptr.data_ptr(), la.n_ctas, la.chunk_cols, la.max_group_acc,
+        la.unit_chunk.data_ptr(), la.cta_unit_ptr.data_ptr(), la.n_ctas, la.chunk_cols, la.n_buffers, la.max_group_acc,
         la.cta_group.data_ptr(), la.group_q_ptr.data_ptr(), la.group_cta_ptr.data_ptr(), la.vbase.data_ptr(),
         la.q_group.data_ptr(), la.long_rows.data_ptr(), la.n_long, la.cta_part_ptr.data_ptr(), la.part.data_ptr(),
         x.data_ptr(), y.data_ptr(), n_cols, la.status.data_ptr(), stream_ptr,

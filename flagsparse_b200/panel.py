@@ -17,8 +17,9 @@ from ._common import _VTYPE
 SM_COUNT_FALLBACK = 148
 CTAS_PER_SM = 1              # one 1024-thread CTA (row block) per SM
 # the kernel is worth its second copy of the matrix only when the extra reads of x and the padding stay small
-MAX_X_OVERHEAD = 0.40       # bytes of x chunks loaded / bytes of entries streamed
+MAX_X_OVERHEAD = 1.3        # bytes of x chunks loaded / bytes of entries streamed
 MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
+N_BUFFERS = 2               # chunks of x in shared memory (fetched N_BUFFERS - 1 units ahead)
 MAX_RUN = 16                # entries of one row inside one unit = rounds per piece (see csrc/spmv_panel.cu)
 MAX_ROW_NNZ = 512
 MIN_NNZ = 1 << 22
@@ -29,14 +30,23 @@ class PanelLayout:
     """Device arrays of the regrouped matrix plus the launch geometry."""
 
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "rb_unit_ptr", "n_row_blocks", "rb_rows", "chunk_cols",
-                 "n_units", "n_pieces", "x_overhead", "slot_overhead", "status")
+                 "n_buffers", "n_units", "n_pieces", "x_overhead", "slot_overhead", "status")
 
     def nbytes(self):
         return sum(t.numel() * t.element_size() for t in (self.val, self.rc, self.unit_piece_ptr, self.unit_chunk,
                                                            self.rb_unit_ptr))
 
 
-def _geometry(dtype, n_rows, device):
+def smem_budget():
+    """Dynamic shared memory one CTA of the panel kernels may use (227 KiB per CTA less the kernel's own tables)."""
+    return 227 * 1024 - int(_lib.lib().fsb_spmv_panel_static_smem_bytes()) - 1024
+
+
+def default_buffers():
+    return int(os.environ.get("FSB_PANEL_BUFFERS", "0")) or N_BUFFERS
+
+
+def _geometry(dtype, n_rows, device, n_buffers):
     L = _lib.lib()
     vt = _VTYPE[dtype]
     sv = 4 if dtype == torch.float32 else 8
@@ -45,9 +55,11 @@ def _geometry(dtype, n_rows, device):
         sms = torch.cuda.get_device_properties(device).multi_processor_count
     except Exception:
         sms = SM_COUNT_FALLBACK
-    budget = (222 * 1024) // CTAS_PER_SM - 1024      # shared memory per CTA, two CTAs per SM
-    fixed = int(L.fsb_spmv_panel_smem_bytes(vt, 0, chunk_cols))
+    budget = smem_budget() // CTAS_PER_SM
+    fixed = int(L.fsb_spmv_panel_smem_bytes(vt, 0, chunk_cols, n_buffers))
     rb_cap = min(49152, (budget - fixed) // sv // 64 * 64)
+    if rb_cap < 1024:
+        return None              # the x buffers alone (nearly) fill the shared memory
     # whole waves of CTAs: the number of row blocks is a multiple of the CTAs the GPU runs at once
     slots_gpu = sms * CTAS_PER_SM
     n_blocks = max(1, -(-n_rows // rb_cap))
@@ -57,18 +69,45 @@ def _geometry(dtype, n_rows, device):
     return vt, sv, chunk_cols, rb_rows, int(L.fsb_spmv_panel_piece_slots())
 
 
+SLAB_NNZ = 1 << 27           # the regrouping works on this many entries at a time (bounds its temporaries)
+
+
+def _slabs(indptr, n_rows, rb_rows, slab_nnz=None):
+    """Row ranges (r0, r1) made of whole row blocks, each holding about slab_nnz entries (at least one block)."""
+    slab_nnz = slab_nnz or SLAB_NNZ
+    n_rb = -(-n_rows // rb_rows)
+    marks = torch.arange(0, n_rb + 1, device=indptr.device) * rb_rows
+    marks[-1] = n_rows
+    at = indptr[marks].to(torch.int64).tolist()        # entries in front of every row block
+    out, b0 = [], 0
+    for b in range(1, n_rb + 1):
+        # close the slab in front of block b when b is the end, or when block b would take it over the limit
+        if b == n_rb or at[b + 1] - at[b0] > slab_nnz:
+            out.append((b0 * rb_rows, min(b * rb_rows, n_rows)))
+            b0 = b
+    return out
+
+
 def estimate_units(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
     """Number of non-empty (row block, column chunk) units, without sorting anything."""
     n_rb = -(-n_rows // rb_rows)
     n_ch = -(-n_cols // chunk_cols)
-    if n_rb * n_ch > (1 << 27):
+    if n_rb * n_ch > (1 << 31):
         return None
-    lens = (indptr[1:] - indptr[:-1]).to(torch.int64)
-    rows = torch.repeat_interleave(torch.arange(n_rows, device=indices.device), lens)
-    key = (rows // rb_rows) * n_ch + indices.to(torch.int64) // chunk_cols
-    mark = torch.zeros(n_rb * n_ch, dtype=torch.bool, device=indices.device)
-    mark[key] = True
-    return int(mark.sum().item())
+    total = 0
+    for r0, r1 in _slabs(indptr, n_rows, rb_rows):
+        e0, e1 = int(indptr[r0]), int(indptr[r1])
+        if e1 == e0:
+            continue
+        lens = (indptr[r0 + 1:r1 + 1] - indptr[r0:r1]).to(torch.int64)
+        rows = torch.repeat_interleave(torch.arange(r0, r1, device=indices.device), lens)
+        b0 = r0 // rb_rows
+        key = (rows // rb_rows - b0) * n_ch + indices[e0:e1].to(torch.int64) // chunk_cols
+        mark = torch.zeros((-(-(r1 - r0) // rb_rows)) * n_ch, dtype=torch.bool, device=indices.device)
+        mark[key] = True
+        total += int(mark.sum().item())
+        del lens, rows, key, mark
+    return total
 
 
 def _cumsum0(counts):
@@ -77,7 +116,8 @@ def _cumsum0(counts):
     return out
 
 
-def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, SLOTS, max_slot_overhead):
+def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, SLOTS, max_slot_overhead,
+                n_buffers=2):
     """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of SLOTS slots and
     lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that follow each
     other with the same key inside one unit form a run, which must not straddle two pieces and may have at most
@@ -133,7 +173,7 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     del lane_, k_, slot, piece, ar
     upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
     del piece_start
-    field = (u_ord[unit_of_entry] & 1) * CW + (cols_p - (cols_p // CW) * CW)
+    field = (u_ord[unit_of_entry] & (n_buffers - 1)) * CW + (cols_p - (cols_p // CW) * CW)
     val = torch.zeros(n_pieces * SLOTS, dtype=data_p.dtype, device=dev)
     val[pos_val] = data_p
     del pos_val
@@ -145,28 +185,23 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     return val, rc, upiece, n_pieces
 
 
-def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False):
-    """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
-    nnz = data.numel()
-    if nnz == 0 or n_rows == 0 or n_cols == 0 or nnz >= 2**31 - 64:
-        return None
-    if not force and (nnz < MIN_NNZ or max_row_nnz > MAX_ROW_NNZ):
-        return None
+def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, SLOTS, NB, max_slot_overhead):
+    """The units and pieces of rows r0 .. r1-1 (whole row blocks).  Returns (val, rc, first piece of each unit + total,
+    chunk of each unit, row block of each unit, number of pieces); () when the rows hold no entry; None when the
+    rows cannot be laid out."""
     dev = data.device
-    vt, sv, CW, RB, SLOTS = _geometry(data.dtype, n_rows, dev)
-    n_rb = -(-n_rows // RB)
-    n_ch = -(-n_cols // CW)
-    if not force:
-        n_units = estimate_units(indices, indptr, n_rows, n_cols, RB, CW)
-        if n_units is None or n_units * CW * sv > MAX_X_OVERHEAD * nnz * (sv + 4):
-            return None
-    lens = (indptr[1:] - indptr[:-1]).to(torch.int64)
-    rows = torch.repeat_interleave(torch.arange(n_rows, device=dev), lens)
-    cols = indices.to(torch.int64)
+    e0, e1 = int(indptr[r0]), int(indptr[r1])
+    if e1 == e0:
+        return ()
+    lens = (indptr[r0 + 1:r1 + 1] - indptr[r0:r1]).to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(r0, r1, device=dev), lens)
+    cols = indices[e0:e1].to(torch.int64)
+    b0 = r0 // RB
     key = (rows // RB) * n_ch + cols // CW
     key_sorted, perm = torch.sort(key, stable=True)   # entries keep their row-major order inside a unit
-    del key
+    del key, lens
     ukey, ucnt = torch.unique_consecutive(key_sorted, return_counts=True)
+    del key_sorted
     n_units = ukey.numel()
     u_rb = ukey // n_ch
     u_ch = ukey % n_ch
@@ -174,23 +209,73 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     unit_of_entry = torch.repeat_interleave(torch.arange(n_units, device=dev), ucnt)
     rows_p = rows[perm]
     cols_p = cols[perm]
-    del rows, cols, key_sorted
-    rb_unit_ptr = torch.searchsorted(u_rb.contiguous(), torch.arange(n_rb + 1, device=dev))
-    # ordinal of a unit inside its row block decides which of the two x buffers it uses
-    u_ord = torch.arange(n_units, device=dev) - rb_unit_ptr[u_rb]
-    packed = pack_pieces(data[perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord, CW,
-                         SLOTS, None if force else MAX_SLOT_OVERHEAD)
-    del rows_p, cols_p, perm, unit_of_entry
+    del rows, cols
+    # ordinal of a unit inside its row block decides which of the x buffers it uses
+    n_b = -(-(r1 - r0) // RB)
+    first_unit = torch.searchsorted(u_rb.contiguous(), torch.arange(b0, b0 + n_b, device=dev))
+    u_ord = torch.arange(n_units, device=dev) - first_unit[u_rb - b0]
+    packed = pack_pieces(data[e0:e1][perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord,
+                         CW, SLOTS, max_slot_overhead, n_buffers=NB)
     if packed is None:
         return None
     val, rc, upiece, n_pieces = packed
+    return val, rc, upiece, u_ch, u_rb, n_pieces
+
+
+def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False):
+    """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
+    nnz = data.numel()
+    if nnz == 0 or n_rows == 0 or n_cols == 0:
+        return None
+    if not force and (nnz < MIN_NNZ or max_row_nnz > MAX_ROW_NNZ):
+        return None
+    dev = data.device
+    NB = default_buffers()
+    geometry = _geometry(data.dtype, n_rows, dev, NB)
+    if geometry is None:
+        return None
+    vt, sv, CW, RB, SLOTS = geometry
+    n_rb = -(-n_rows // RB)
+    n_ch = -(-n_cols // CW)
+    if not force:
+        n_units = estimate_units(indices, indptr, n_rows, n_cols, RB, CW)
+        if n_units is None or n_units * CW * sv > MAX_X_OVERHEAD * nnz * (sv + 4):
+            return None
+    vals, rcs, upieces, chunks, blocks = [], [], [], [], []
+    piece_base = 0
+    for r0, r1 in _slabs(indptr, n_rows, RB):
+        part = _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, SLOTS, NB,
+                           None if force else MAX_SLOT_OVERHEAD)
+        if part is None:
+            return None
+        if part == ():
+            continue                 # no entries in these rows
+        val_s, rc_s, upiece_s, u_ch_s, u_rb_s, n_pieces_s = part
+        vals.append(val_s)
+        rcs.append(rc_s)
+        upieces.append(upiece_s[:-1] + piece_base)
+        chunks.append(u_ch_s)
+        blocks.append(u_rb_s)
+        piece_base += n_pieces_s
+    n_pieces = piece_base
+    if n_pieces >= 2**31 - 1:
+        return None
+    val, rc = (t[0] if len(t) == 1 else torch.cat(t) for t in (vals, rcs))
+    del vals, rcs
+    upiece = torch.cat(upieces + [torch.tensor([n_pieces], dtype=torch.int64, device=dev)])
+    u_ch = torch.cat(chunks)
+    u_rb = torch.cat(blocks)
+    n_units = u_ch.numel()
+    rb_unit_ptr = torch.searchsorted(u_rb.contiguous(), torch.arange(n_rb + 1, device=dev))
+    if not force and n_pieces * SLOTS > MAX_SLOT_OVERHEAD * nnz + 4096 * len(upieces):
+        return None
 
     lay = PanelLayout()
     lay.val, lay.rc = val, rc
     lay.unit_piece_ptr = upiece.to(torch.int32)
     lay.unit_chunk = u_ch.to(torch.int32)
     lay.rb_unit_ptr = rb_unit_ptr.to(torch.int32)
-    lay.n_row_blocks, lay.rb_rows, lay.chunk_cols = n_rb, RB, CW
+    lay.n_row_blocks, lay.rb_rows, lay.chunk_cols, lay.n_buffers = n_rb, RB, CW, NB
     lay.n_units, lay.n_pieces = n_units, n_pieces
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)
@@ -203,6 +288,7 @@ def launch_panel(layout, x, y, n_rows, n_cols, stream_ptr):
     rc = L.fsb_spmv_csr_panel(
         _VTYPE[layout.val.dtype], layout.val.data_ptr(), layout.rc.data_ptr(), layout.unit_piece_ptr.data_ptr(),
         layout.unit_chunk.data_ptr(), layout.rb_unit_ptr.data_ptr(), layout.n_row_blocks, layout.rb_rows,
-        layout.chunk_cols, x.data_ptr(), y.data_ptr(), n_rows, n_cols, layout.status.data_ptr(), stream_ptr,
+        layout.chunk_cols, layout.n_buffers, x.data_ptr(), y.data_ptr(), n_rows, n_cols, layout.status.data_ptr(),
+        stream_ptr,
     )
     _lib.check(rc, "fsb_spmv_csr_panel")

@@ -87,9 +87,10 @@ class ShardedCsrSpmv:
         if local_spmv is None:
             from .spmv_csr import _prepare_spmv_csr
 
-            # the peer-store epilogue exists for the vector and the stream kernel only: no regrouped layouts there
+            # the peer-store epilogue exists for the vector, the stream and the panel kernel, not for the split
+            # of long rows
             self.prepared = _prepare_spmv_csr(data, indices, indptr, (self.n_local, self.n_cols), 256, None,
-                                              reuse_expected=mode != "peer")
+                                              reuse_expected=True, allow_split=mode != "peer")
         self.mode = mode
         self._y = None
         self._symm = None
@@ -110,8 +111,7 @@ class ShardedCsrSpmv:
     def _setup_peer(self):
         import torch.distributed._symmetric_memory as symm_mem
 
-        # the epilogue with peer stores exists for the vector and the stream kernel; a shard prepared for the
-        # panel kernel uses the vector kernel here (its rows are uniform by construction)
+        # a shard prepared for the panel kernel has its own entry point with peer stores
         self._peer_algo = _lib.FSB_SPMV_STREAM if self.prepared.algo == _lib.FSB_SPMV_STREAM else _lib.FSB_SPMV_VECTOR
         group = self.group if self.group is not None else dist.group.WORLD
         # two result buffers used alternately: a rank may start the next product while its peers still
@@ -162,7 +162,17 @@ class ShardedCsrSpmv:
         L = _lib.lib()
         base = self._parity * self._stride
         self._parity ^= 1
-        if self.n_local > 0:
+        if self.n_local > 0 and p.algo == _lib.FSB_SPMV_PANEL and p.panel is not None:
+            la = p.panel
+            with torch.cuda.device(self.device):
+                rc = L.fsb_spmv_csr_panel_scatter(
+                    _VTYPE[la.val.dtype], la.val.data_ptr(), la.rc.data_ptr(), la.unit_piece_ptr.data_ptr(),
+                    la.unit_chunk.data_ptr(), la.rb_unit_ptr.data_ptr(), la.n_row_blocks, la.rb_rows, la.chunk_cols,
+                    la.n_buffers, _ptr(x), self._peer_ptrs.data_ptr(), self.world, base + self.row_start, p.n_rows,
+                    p.n_cols, la.status.data_ptr(), _stream_ptr(self.device),
+                )
+            _lib.check(rc, "fsb_spmv_csr_panel_scatter")
+        elif self.n_local > 0:
             with torch.cuda.device(self.device):
                 rc = L.fsb_spmv_csr_scatter(
                     _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],

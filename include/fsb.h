@@ -125,23 +125,38 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
  * flagsparse_b200/panel.py): entries grouped into units = (block of rb_rows rows) x (chunk of chunk_cols
  * columns), row-major inside a unit, each unit cut into pieces of fsb_spmv_panel_piece_slots() slots so
  * that no row's entries straddle two pieces.
- *   val[s], rc[s]        per slot: value and packed word (local row << 16 | parity * chunk_cols + local
- *                        column), parity = ordinal of the unit inside its row block modulo 2; unused
+ *   val[s], rc[s]        per slot: value and packed word (local row << 16 | buffer * chunk_cols + local
+ *                        column), buffer = ordinal of the unit inside its row block modulo n_buffers; unused
  *                        slots carry local row 0xFFFF
+ *   n_buffers            2, 4 or 8 chunks of x in shared memory (n_buffers * chunk_cols <= 65536): chunks are
+ *                        fetched n_buffers - 1 units ahead of their use
  *   unit_piece_ptr       pieces [unit_piece_ptr[u], unit_piece_ptr[u+1]) belong to unit u
  *   unit_chunk           column chunk of unit u
  *   rb_unit_ptr          units [rb_unit_ptr[b], rb_unit_ptr[b+1]) belong to row block b, in chunk order
- * One CTA per row block keeps the block's y accumulators and two chunks of x in shared memory
- * (fsb_spmv_panel_smem_bytes() must fit in 227 KiB; rb_rows < 65535).  Another stand-in for the launches of
+ * One CTA per row block keeps the block's y accumulators and n_buffers chunks of x in shared memory
+ * (fsb_spmv_panel_smem_bytes() + fsb_spmv_panel_static_smem_bytes() must fit in 227 KiB; rb_rows < 65535).  Another stand-in for the launches of
  * _triton_spmv_csr_impl_opt_prepared (spmv_csr.py:329-376), for matrices whose rows span few column chunks.
  * status: optional device int32, set non-zero if a bounded wait on a bulk copy of x ran out.
  */
 int fsb_spmv_panel_piece_slots(void);
-size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols);
+size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers);
+size_t fsb_spmv_panel_static_smem_bytes(void);
 int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                        const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
-                       int32_t rb_rows, int32_t chunk_cols, const void* x, void* y, int64_t n_rows,
-                       int64_t n_cols, int32_t* status, void* stream);
+                       int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x, void* y,
+                       int64_t n_rows, int64_t n_cols, int32_t* status, void* stream);
+
+/*
+ * The same product for one shard of a row-sharded matrix: row i of the shard is stored to
+ * y_peers[p][row_offset + i] for every p in [0, n_peers) -- y_peers is a DEVICE array of n_peers device pointers
+ * (this GPU's buffer and the peer-mapped buffers of the other GPUs), as for fsb_spmv_csr_scatter.  No counterpart
+ * in the reference (single GPU).
+ */
+int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                               const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
+                               int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x,
+                               void* const* y_peers, int n_peers, int64_t row_offset, int64_t n_rows,
+                               int64_t n_cols, int32_t* status, void* stream);
 
 /*
  * Row-group form of the panel product, for the LONG rows of a skewed matrix: y[long_rows[q]] = (A x)[long_rows[q]]
@@ -151,8 +166,8 @@ int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int
  * The picked rows are cut into groups; row q owns accumulators vbase[q] .. vbase[q+1]-1 ("virtual rows": at most
  * 16 entries of a virtual row in one column chunk) and the packed word of a slot holds the virtual row relative
  * to its group.  The units (group x column chunk) are ordered by group, then chunk, and dealt to n_ctas CTAs:
- *   cta_unit_ptr         units [cta_unit_ptr[c], cta_unit_ptr[c+1]) belong to CTA c (parity of a slot's packed
- *                        word = ordinal of the unit inside its CTA modulo 2)
+ *   cta_unit_ptr         units [cta_unit_ptr[c], cta_unit_ptr[c+1]) belong to CTA c (buffer of a slot's packed
+ *                        word = ordinal of the unit inside its CTA modulo n_buffers)
  *   cta_group            group of CTA c;  group_cta_ptr: CTAs [group_cta_ptr[g], group_cta_ptr[g+1]) work on group g
  *   group_q_ptr          rows q in [group_q_ptr[g], group_q_ptr[g+1]) form group g;  q_group[q]: group of row q
  *   max_group_acc        largest number of accumulators of a group (shared memory: fsb_spmv_panel_smem_bytes)
@@ -163,7 +178,7 @@ int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int
  */
 int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                               const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
-                              int32_t chunk_cols, int32_t max_group_acc, const int32_t* cta_group,
+                              int32_t chunk_cols, int32_t n_buffers, int32_t max_group_acc, const int32_t* cta_group,
                               const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
                               const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
                               const int64_t* cta_part_ptr, void* part, const void* x, void* y, int64_t n_cols,

@@ -45,7 +45,7 @@ def _evaluate_long(lay, x):
         assert 0 < n_acc <= lay.max_group_acc
         acc = np.zeros(n_acc)
         for u in range(cup[c], cup[c + 1]):
-            parity = (u - cup[c]) & 1
+            parity = (u - cup[c]) & (lay.n_buffers - 1)
             per_acc = {}
             for pc in range(upp[u], upp[u + 1]):
                 w = rc[pc * SLOTS + (k // 4) * 128 + ln * 4 + k % 4]

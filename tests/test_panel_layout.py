@@ -24,7 +24,7 @@ def _evaluate(lay, x, n_rows, n_cols, slots):
     for b in range(lay.n_row_blocks):
         assert np.all(np.diff(uch[rbp[b]:rbp[b + 1]]) > 0)   # units of a row block in chunk order
         for u in range(rbp[b], rbp[b + 1]):
-            parity = (u - rbp[b]) & 1
+            parity = (u - rbp[b]) & (lay.n_buffers - 1)
             rows_in_unit = []
             for pc in range(upp[u], upp[u + 1]):
                 # undo the interleaving: slot = 16 * lane + k
@@ -67,7 +67,8 @@ def test_layout_of_a_banded_matrix(fsb_lib, vdt):
     ref, mag = O.spmv_f64(d.numpy(), i.numpy(), p.numpy(), (spec.n_rows, spec.n_cols), x)
     assert np.allclose(y, ref, rtol=0, atol=1e-9)
     vt = 0 if vdt == "float32" else 1
-    assert fsb_lib.fsb_spmv_panel_smem_bytes(vt, lay.rb_rows, lay.chunk_cols) <= 227 * 1024
+    assert (fsb_lib.fsb_spmv_panel_smem_bytes(vt, lay.rb_rows, lay.chunk_cols, lay.n_buffers)
+            + fsb_lib.fsb_spmv_panel_static_smem_bytes()) <= 227 * 1024
     assert lay.slot_overhead < 1.5  # a small matrix: the last piece of each unit is mostly padding
 
 
@@ -98,3 +99,37 @@ def test_selection_rules(fsb_lib):
     spec3 = S.config_spec("c3").scaled(1 << 18)
     d, i, p = (torch.from_numpy(a) for a in S.generate_csr(spec3, None))
     assert panel.estimate_units(i, p, spec3.n_rows, spec3.n_cols, 2048, 4096) > 0.9 * 128 * 64
+
+
+def test_layout_built_in_slabs_equals_layout_built_at_once(fsb_lib, monkeypatch):
+    spec = S.config_spec("c2").scaled(120000)
+    d, i, p = S.generate_csr(spec, None)
+    td, ti, tp = torch.from_numpy(d), torch.from_numpy(i), torch.from_numpy(p)
+    whole = panel.build_panel_layout(td, ti, tp, spec.n_rows, spec.n_cols, int(np.diff(p).max()), force=True)
+    monkeypatch.setattr(panel, "SLAB_NNZ", d.size // 7)
+    slabs = panel._slabs(tp, spec.n_rows, whole.rb_rows)
+    assert len(slabs) > 3 and slabs[0][0] == 0 and slabs[-1][1] == spec.n_rows
+    assert all(a[1] == b[0] and a[0] % whole.rb_rows == 0 for a, b in zip(slabs, slabs[1:]))
+    parts = panel.build_panel_layout(td, ti, tp, spec.n_rows, spec.n_cols, int(np.diff(p).max()), force=True)
+    for name in ("val", "rc", "unit_piece_ptr", "unit_chunk", "rb_unit_ptr"):
+        assert torch.equal(getattr(whole, name), getattr(parts, name)), name
+    assert (whole.n_units, whole.n_pieces) == (parts.n_units, parts.n_pieces)
+    assert panel.estimate_units(ti, tp, spec.n_rows, spec.n_cols, whole.rb_rows, whole.chunk_cols) == whole.n_units
+
+
+@pytest.mark.parametrize("n_buffers", [4, 8])
+def test_layout_with_more_x_buffers(fsb_lib, monkeypatch, n_buffers):
+    monkeypatch.setattr(panel, "N_BUFFERS", n_buffers)
+    spec = S.config_spec("c2").scaled(120000)
+    d, i, p = S.generate_csr(spec, None)
+    x = S.dense_vector(spec, spec.n_cols)
+    lay = panel.build_panel_layout(torch.from_numpy(d), torch.from_numpy(i), torch.from_numpy(p), spec.n_rows,
+                                   spec.n_cols, int(np.diff(p).max()), force=True)
+    if n_buffers == 8:
+        assert lay is None          # eight float32 chunks of 8192 columns leave no room for the accumulators
+        return
+    assert lay.n_buffers == n_buffers
+    y, seen = _evaluate(lay, x.astype(np.float64), spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots())
+    assert seen == d.size
+    ref, mag = O.spmv_f64(d, i, p, (spec.n_rows, spec.n_cols), x)
+    assert O.max_bound_ratio(y, ref, mag) <= 1e-12

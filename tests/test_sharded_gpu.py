@@ -44,8 +44,9 @@ def _worker(rank, world, port, result_dir):
         d, i, p = S.generate_csr(spec, device, indptr_dtype="int64", row_range=(r0, r1))
         x = S.dense_vector(spec, spec.n_cols, device)
         results = {}
-        # the peer-store epilogue exists for the vector kernel (picked for these uniform rows) and the stream kernel
-        for mode, algo in (("nccl", None), ("peer", None), ("peer", "stream")):
+        # the peer-store epilogue exists for the vector kernel (picked for these uniform rows), the stream kernel
+        # and the panel kernel
+        for mode, algo in (("nccl", None), ("peer", None), ("peer", "stream"), ("peer", "panel"), ("nccl", "panel")):
             if algo:
                 os.environ["FSB_SPMV_ALGO"] = algo
             try:
@@ -61,6 +62,10 @@ def _worker(rank, world, port, result_dir):
         assert torch.equal(results[("nccl", None)], results[("peer", None)])
         # the stream kernel adds in another order: held to the oracle bound by the parent, close to the others here
         assert torch.allclose(results[("nccl", None)], results[("peer", "stream")], rtol=1e-4, atol=1e-4)
+        # the panel kernel with local stores + NCCL and with peer stores: the same sums, the same bits
+        assert torch.equal(results[("nccl", "panel")], results[("peer", "panel")])
+        assert torch.allclose(results[("nccl", None)], results[("peer", "panel")], rtol=1e-4, atol=1e-4)
+        np.save(os.path.join(result_dir, f"p{rank}.npy"), results[("peer", "panel")].cpu().numpy())
         np.save(os.path.join(result_dir, f"y{rank}.npy"), results[("peer", None)].cpu().numpy())
         np.save(os.path.join(result_dir, f"n{rank}.npy"), results[("peer", "stream")].cpu().numpy())
     finally:
@@ -85,3 +90,6 @@ def test_two_ranks_nccl_and_peer(cuda, fsb_lib, tmp_path):
     x = S.dense_vector(spec, spec.n_cols) * np.float32(3.0)
     assert_spmv_ok(y0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores, vector kernel")
     assert_spmv_ok(n0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores, stream kernel")
+    p0, p1 = np.load(tmp_path / "p0.npy"), np.load(tmp_path / "p1.npy")
+    assert np.array_equal(p0, p1)
+    assert_spmv_ok(p0, d, i, p, (spec.n_rows, spec.n_cols), x, what="two ranks, peer stores, panel kernel")

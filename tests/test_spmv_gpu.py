@@ -100,8 +100,9 @@ def test_panel_kernel_on_banded_matrix(cuda, fsb_lib, vdt, idt):
     with env(FSB_SPMV_ALGO=None if vdt == "float32" else "panel"):
         prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
     assert prep.algo == _lib.FSB_SPMV_PANEL and prep.panel is not None
-    # a band as wide as the matrix is short is not worth regrouping: the vector kernel stays
-    wide = S.config_spec("c2").scaled(1 << 18)
+    # columns spread over the whole matrix are not worth regrouping (every unit would load a chunk of x for a few
+    # hundred entries): the vector kernel stays
+    wide = S.config_spec("c4")
     dw, iw, pw = S.generate_csr(wide, "cuda:0", value_dtype=vdt)
     assert fs.prepare_spmv_csr(dw, iw, pw, (wide.n_rows, wide.n_cols)).algo == _lib.FSB_SPMV_VECTOR
     del dw, iw, pw
