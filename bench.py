@@ -35,7 +35,8 @@ FALLBACK_HBM_GBS = 6650.0
 # summarised under profiles/ (None until a capture exists for the workload)
 NCU_TRAFFIC_BYTES = {
     "c2": 1.102e9,      # profiles/spmv_panel_c2_f32.md
-    "c3": 3.534e9,      # profiles/spmv_stream_c3_f32.md
+    "c2f64": 1.678e9,   # profiles/spmv_panel_c2_f64.md
+    "c3": 2.950e9,      # profiles/spmv_panel_groups_c3_f32.md: stream kernel on the short rows + row-group panel kernel
     "c4n32": 1.290e9,   # profiles/spmm_tile_c4_f32.md
     "c4n128": 7.951e9,  # profiles/spmm_tile_c4_f32.md
 }
