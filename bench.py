@@ -18,6 +18,7 @@ C) once, with the byte widths the kernels actually stream (never more than the c
 """
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -335,7 +336,8 @@ def run_ours(args, workload):
     torch.cuda.set_device(local_rank)
     device = f"cuda:{local_rank}"
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device(device))
+        # a rank that never reaches a collective ends the run after three minutes instead of ten
+        dist.init_process_group("nccl", device_id=torch.device(device), timeout=datetime.timedelta(seconds=180))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
 
@@ -447,11 +449,21 @@ def run_ours(args, workload):
     with ClockSampler(physical_gpu_index(local_rank)) as clocks:
         elapsed = timed_region(torch, step, args.steps, barrier)
         # keep the same load on the GPU until the sampler has seen enough of it (not part of any timing)
-        t_more = time.perf_counter()
-        while len(clocks.samples) < 12 and time.perf_counter() - t_more < 2.0:
-            for _ in range(20):
+        if world > 1:
+            # every sharded step holds a collective (the exchange of y), so all ranks must run the SAME number of
+            # extra steps: derive it from the slowest rank's step time, never from a rank's own clock or sampler
+            t = torch.tensor([elapsed], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            slowest = max(float(t[0]) / args.steps, 1e-6)
+            for _ in range(int(min(2000, max(20, 0.3 / slowest)))):
                 step()
             torch.cuda.synchronize()
+        else:
+            t_more = time.perf_counter()
+            while len(clocks.samples) < 12 and time.perf_counter() - t_more < 2.0:
+                for _ in range(20):
+                    step()
+                torch.cuda.synchronize()
     for _ in range(3):
         e2e_step()
     e2e_elapsed = timed_region(torch, e2e_step, args.steps, barrier)
