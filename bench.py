@@ -420,7 +420,9 @@ def run_ours(args, workload):
             d, i, p = S.generate_csr(spec, device, value_dtype=vdt, index_dtype=idt, indptr_dtype=pdt, row_range=(r0, r1))
             op = fs.ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=args.exchange)
             step = lambda: op.matvec(x)  # noqa: E731
-            launches_per_step = 2  # tile kernel + fix-up (the barrier / NCCL kernels are not ours)
+            # stream kernel + fix-up, or one vector / panel kernel (the barrier / NCCL kernels are not ours)
+            launches_per_step = 2 if op.prepared.algo == _lib.FSB_SPMV_STREAM else 1
+            extra["kernel"] = op.prepared.opt_buckets[0]["kind"]
             si, sp_ = op.prepared.kernel_indices.element_size(), op.prepared.kernel_indptr.element_size()
             extra["exchange"] = op.mode
             extra["shard_nnz"] = d.numel()
