@@ -16,7 +16,9 @@ the reference's @triton.jit kernels:
   COO SpMM       _triton_spmm_coo_impl               (src/flagsparse/sparse_operations/spmm_coo.py:533-570) after
                  _prepare_spmm_coo_canonical_prepared (:78-105), as _run_spmm_coo_route (:626-668) does
 plus the pure host helpers (_resolve_spmm_alg1_launch_config, _select_spmm_opt_block_n,
-coo_to_csr_for_spmv).  `--only coo` regenerates the COO fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
+coo_to_csr_for_spmv), and the Matrix Market loader of the reference's benchmark scripts
+  load_mtx_to_csr_torch  (tests/test_spmv.py:29-103 and tests/test_spmm.py:163-268 of the reference)
+on the small files of tests/golden/mtx/.  `--only coo` / `--only mtx` regenerate those fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
 synthetic generator changes.  Nothing here is imported by the package, the tests or the benchmark.
 """
 
@@ -190,6 +192,32 @@ def make_coo(index, V, MC):
         print("coo", name, val.size, index["coo"][name], flush=True)
 
 
+def make_mtx(index, reference_root):
+    """CSR arrays the reference's two loaders produce for tests/golden/mtx/*.mtx (float32 and float64, on CPU)."""
+    import glob
+    import importlib.util
+
+    loaders = {}
+    for name in ("test_spmv", "test_spmm"):
+        spec = importlib.util.spec_from_file_location(f"ref_{name}", os.path.join(reference_root, "tests", f"{name}.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        loaders[name] = mod.load_mtx_to_csr_torch
+    index["mtx"] = {}
+    for path in sorted(glob.glob(os.path.join(HERE, "mtx", "*.mtx"))):
+        name = os.path.splitext(os.path.basename(path))[0]
+        out = {}
+        for dt, tag in ((torch.float32, "f32"), (torch.float64, "f64")):
+            a = loaders["test_spmv"](path, dtype=dt, device=torch.device("cpu"))
+            b = loaders["test_spmm"](path, dtype=dt, device=torch.device("cpu"))
+            assert a[3] == b[3] and all(torch.equal(u, v) for u, v in zip(a[:3], b[:3])), "the two loaders disagree"
+            out[f"data_{tag}"] = a[0].numpy()
+            out["indices"], out["indptr"], out["shape"] = a[1].numpy(), a[2].numpy(), np.asarray(a[3])
+        np.savez_compressed(os.path.join(HERE, f"mtx_{name}.npz"), **out)
+        index["mtx"][name] = {"nnz": int(out["indices"].size), "shape": [int(v) for v in out["shape"]]}
+        print("mtx", name, index["mtx"][name], flush=True)
+
+
 def host_helper_goldens(R, M):
     g = {"alg1": [], "opt_block_n": {}, "coo": {}}
     for n in (1, 4, 5, 8, 9, 16, 17, 24, 32, 33, 48, 64, 65, 96, 128, 256):
@@ -215,7 +243,7 @@ def host_helper_goldens(R, M):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
-    ap.add_argument("--only", choices=("all", "coo"), default="all")
+    ap.add_argument("--only", choices=("all", "coo", "mtx"), default="all")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from flagsparse.sparse_operations import spmm_coo as MC  # noqa: E402
@@ -224,10 +252,13 @@ def main():
     from flagsparse.sparse_operations import spmv_csr as R  # noqa: E402
 
     index_path = os.path.join(HERE, "index.json")
-    if args.only == "coo":
+    if args.only in ("coo", "mtx"):
         with open(index_path) as f:
             index = json.load(f)
-        make_coo(index, V, MC)
+        if args.only == "coo":
+            make_coo(index, V, MC)
+        else:
+            make_mtx(index, args.reference)
         with open(index_path, "w") as f:
             json.dump(index, f, indent=1, sort_keys=True)
         return
@@ -245,6 +276,7 @@ def main():
         index["spmm"][name] = {"nnz": int(data.size), "buckets": meta}
         print("spmm", name, data.size, meta, flush=True)
     make_coo(index, V, MC)
+    make_mtx(index, args.reference)
     index["host"] = host_helper_goldens(R, M)
     with open(index_path, "w") as f:
         json.dump(index, f, indent=1, sort_keys=True)
