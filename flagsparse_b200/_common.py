@@ -1,18 +1,19 @@
 """Dtype tables, limits and tolerances shared by the CSR SpMV / SpMM host code.
 
 Mirrors the conventions of the reference's src/flagsparse/sparse_operations/_common.py:22-31 (dtype
-whitelists, int32 index limit) and :76-85 (allclose tolerances).  Only float32 / float64 values are
-computed by this package; the other value dtypes of the reference's whitelist are recognised so that the
-error raised for them says what is missing instead of calling them invalid.
+whitelists, int32 index limit) and :76-85 (allclose tolerances).  The CUDA kernels compute float32 and float64;
+the other four value dtypes of the reference's whitelist run through them by widening or by splitting complex
+values into real and imaginary matrices (widetypes.py), on the entry points where the reference accepts them.
 """
 
 import torch
 
 from . import _lib
 
-SUPPORTED_VALUE_DTYPES = (torch.float32, torch.float64)
-# value dtypes the reference also accepts on its base paths; not implemented by the CUDA kernels here
-REFERENCE_ONLY_VALUE_DTYPES = (torch.float16, torch.bfloat16, torch.complex64, torch.complex128)
+SUPPORTED_VALUE_DTYPES = (torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.complex64,
+                          torch.complex128)
+# what the kernels themselves compute in; the other value dtypes are widened or split on the host
+NATIVE_VALUE_DTYPES = (torch.float32, torch.float64)
 SUPPORTED_INDEX_DTYPES = (torch.int32, torch.int64)
 _INDEX_LIMIT_INT32 = 2**31 - 1
 
@@ -23,11 +24,6 @@ _ITYPE = {torch.int32: _lib.FSB_I32, torch.int64: _lib.FSB_I64}
 def _check_value_dtype(dtype, what="data"):
     if dtype in SUPPORTED_VALUE_DTYPES:
         return
-    if dtype in REFERENCE_ONLY_VALUE_DTYPES:
-        raise TypeError(
-            f"{what} dtype {dtype} is accepted by the reference but not by the sm_100a kernels of this "
-            "package, which compute float32 and float64 only"
-        )
     raise TypeError(
         f"{what} dtype must be one of: float16, bfloat16, float32, float64, complex64, complex128"
     )

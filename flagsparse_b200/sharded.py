@@ -77,12 +77,15 @@ class ShardedCsrSpmv:
         self._local_spmv = local_spmv
         if mode == "auto":
             # the fused exchange needs the CUDA kernels, several ranks and something to multiply
-            fused_ok = local_spmv is None and self.world > 1 and data.is_cuda
+            fused_ok = (local_spmv is None and self.world > 1 and data.is_cuda
+                        and data.dtype in (torch.float32, torch.float64))
             mode = "peer" if fused_ok else "nccl"
         if mode not in ("nccl", "peer"):
             raise ValueError("mode must be 'auto', 'nccl' or 'peer'")
         if mode == "peer" and local_spmv is not None:
             raise ValueError("mode 'peer' fuses the exchange into the CUDA kernel; it cannot take local_spmv")
+        if mode == "peer" and data.dtype not in (torch.float32, torch.float64):
+            raise TypeError("mode 'peer' needs float32 or float64 values (the kernels with peer stores compute those)")
         self.prepared = None
         if local_spmv is None:
             from .spmv_csr import _prepare_spmv_csr

@@ -13,7 +13,7 @@ import time
 
 import torch
 
-from . import _lib
+from . import _lib, widetypes
 from ._common import (
     SUPPORTED_INDEX_DTYPES,
     _INDEX_LIMIT_INT32,
@@ -154,10 +154,11 @@ class PreparedCsrSpmmOpt:
         "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "max_row_nnz",
         "row_buckets", "supports_opt", "long_part_rows", "long_part_starts", "long_part_ends",
         "long_row_ids", "long_row_part_ptr", "long_row_fallback_only", "stats", "tile_nnz", "tile_row",
-        "_scratch", "_status", "_row_lengths",
+        "_scratch", "_status", "_row_lengths", "wide",
     )
 
-    def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, tile_nnz, tile_row):
+    def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, tile_nnz, tile_row,
+                 wide=None):
         dev = data.device
         self.data = data
         self.kernel_indices = kernel_indices
@@ -181,6 +182,8 @@ class PreparedCsrSpmmOpt:
         self._scratch = {}
         self._status = None
         self._row_lengths = None
+        # float16 / bfloat16 / complex values: (kind, prepared real matrices) the products go through (widetypes.py)
+        self.wide = wide
 
     @property
     def row_lengths(self):
@@ -209,6 +212,12 @@ def prepare_spmm_csr_opt(data, indices, indptr, shape):
         data, indices, indptr, shape
     )
     nnz = data.numel()
+    if data.dtype in widetypes.WIDE_DTYPES:
+        # computed in a wider real type, as the reference's base path does (:525-560): one real matrix per part
+        kind, reals = widetypes.split_values(data)
+        parts = [prepare_spmm_csr_opt(r, kernel_indices, kernel_indptr, shape) for r in reals]
+        return PreparedCsrSpmmOpt(data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats,
+                                  parts[0].tile_nnz, None, wide=(kind, parts))
     tile_nnz, tile_row = 0, None
     if nnz > 0 and n_rows > 0:
         tile_nnz = int(_lib.lib().fsb_spmm_tile_nnz(_VTYPE[data.dtype]))
@@ -251,6 +260,21 @@ def _check_out(out, device, shape, dtype, device_msg):
 def _run_spmm(prepared, B, out, return_time):
     dev, dtype = prepared.data.device, prepared.data.dtype
     shape = (prepared.n_rows, int(B.shape[1]))
+    if prepared.wide is not None:
+        kind, parts = prepared.wide
+        t0 = None
+        if return_time:
+            torch.cuda.synchronize(dev)
+            t0 = time.perf_counter()
+        C = widetypes.product(kind, parts, B, _spmm_launch, shape, dtype)
+        elapsed_ms = None
+        if return_time:
+            torch.cuda.synchronize(dev)
+            elapsed_ms = (time.perf_counter() - t0) * 1000.0
+        if out is not None:
+            out.copy_(C)
+            C = out
+        return (C, elapsed_ms) if return_time else C
     direct = out is not None and out.is_contiguous()
     C = out if direct else torch.empty(shape, dtype=dtype, device=dev)
     t0 = None

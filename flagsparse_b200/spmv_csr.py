@@ -12,7 +12,7 @@ import time
 
 import torch
 
-from . import _lib
+from . import _lib, widetypes
 from ._common import (
     SUPPORTED_INDEX_DTYPES,
     _INDEX_LIMIT_INT32,
@@ -88,12 +88,12 @@ class PreparedCsrSpmv:
     __slots__ = (
         "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "block_nnz",
         "max_segments", "max_row_nnz", "opt_buckets", "supports_opt", "stats", "algo", "tuning",
-        "tile_nnz", "tile_row", "scratch", "panel", "long_rows",
+        "tile_nnz", "tile_row", "scratch", "panel", "long_rows", "wide",
     )
 
     def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, block_nnz,
                  max_segments, max_row_nnz, stats, algo, tuning, tile_nnz, tile_row, scratch, panel=None,
-                 long_rows=None):
+                 long_rows=None, wide=None):
         self.data = data
         self.kernel_indices = kernel_indices
         self.kernel_indptr = kernel_indptr
@@ -112,6 +112,8 @@ class PreparedCsrSpmv:
         self.scratch = scratch
         self.panel = panel
         self.long_rows = long_rows   # (prepared short-row part, LongRowLayout) when the long rows were split off
+        # float16 / bfloat16 / complex values: (kind, prepared real matrices) the products go through (widetypes.py)
+        self.wide = wide
         n_tiles = 0 if tile_row is None else tile_row.numel() - 1
         kind = {_lib.FSB_SPMV_STREAM: "stream", _lib.FSB_SPMV_PANEL: "panel"}.get(algo, "vector")
         if long_rows is not None:
@@ -216,6 +218,17 @@ def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reu
     max_row_nnz = stats.max_row_nnz
     block_nnz_use, max_segments_use = _resolve_block_nnz(max_row_nnz, block_nnz, max_segments)
     nnz = data.numel()
+    if data.dtype in widetypes.WIDE_DTYPES:
+        # the reference computes these in a wider real type too (:496-535); one prepared real matrix per part
+        kind, reals = widetypes.split_values(data)
+        parts = [_prepare_spmv_csr(r, kernel_indices, kernel_indptr, shape, block_nnz, max_segments, reuse_expected,
+                                   allow_split) for r in reals]
+        return PreparedCsrSpmv(
+            data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape, n_rows=n_rows,
+            n_cols=n_cols, block_nnz=block_nnz_use, max_segments=max_segments_use, max_row_nnz=max_row_nnz,
+            stats=stats, algo=parts[0].algo, tuning=parts[0].tuning, tile_nnz=parts[0].tile_nnz, tile_row=None,
+            scratch=None, wide=(kind, parts),
+        )
     algo = _select_spmv_algo(n_rows, nnz, max_row_nnz)
     tuning = int(os.environ.get("FSB_SPMV_TUNING", "0"))
     tile_nnz, tile_row, scratch, panel_layout = 0, None, None, None
@@ -303,6 +316,21 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
     dtype = prepared.data.dtype
     if out is not None and (out.shape != (prepared.n_rows,) or out.dtype != dtype):
         raise ValueError("out shape/dtype must match result")
+    if prepared.wide is not None:
+        kind, parts = prepared.wide
+        t0 = None
+        if return_time:
+            torch.cuda.synchronize(dev)
+            t0 = time.perf_counter()
+        y = widetypes.product(kind, parts, x, _spmv_launch, (prepared.n_rows,), dtype)
+        elapsed_ms = None
+        if return_time:
+            torch.cuda.synchronize(dev)
+            elapsed_ms = (time.perf_counter() - t0) * 1000.0
+        if out is not None:
+            out.copy_(y)
+            y = out
+        return (y, elapsed_ms) if return_time else y
     # write straight into `out` when that is safe, else into a fresh vector that is copied over
     direct = out is not None and out.is_cuda and out.device == dev and out.is_contiguous()
     y = out if direct else torch.empty(prepared.n_rows, dtype=dtype, device=dev)

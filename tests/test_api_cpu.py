@@ -113,13 +113,13 @@ def test_spmm_validation_on_cpu_tensors():
 def test_value_dtype_messages():
     from flagsparse_b200._common import _check_value_dtype
 
-    for ok in (torch.float32, torch.float64):
+    for ok in (torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.complex64, torch.complex128):
         _check_value_dtype(ok)
-    for ref_only in (torch.float16, torch.bfloat16, torch.complex64, torch.complex128):
-        with pytest.raises(TypeError, match="accepted by the reference"):
-            _check_value_dtype(ref_only)
-    with pytest.raises(TypeError, match="must be one of"):
-        _check_value_dtype(torch.int32)
+    assert fs.SUPPORTED_VALUE_DTYPES == (torch.float16, torch.bfloat16, torch.float32, torch.float64,
+                                         torch.complex64, torch.complex128)       # the reference's whitelist
+    for bad in (torch.int32, torch.int64, torch.bool, torch.uint8):
+        with pytest.raises(TypeError, match="must be one of"):
+            _check_value_dtype(bad)
     assert fs._tolerance_for_dtype(torch.float32) == (1e-6, 1e-5)
     assert fs._tolerance_for_dtype(torch.float64) == (1e-10, 1e-8)
 

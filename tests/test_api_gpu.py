@@ -53,7 +53,9 @@ def test_spmm_negative_cases(tiny, cuda, fsb_lib):
         (lambda: fs.flagsparse_spmm_csr(ld, li, lp, lB, lshape, block_nnz=128, max_segments=4), ValueError),
         # a few more from the checks in the reference's source
         (lambda: fs.flagsparse_spmm_csr(data, t([-1, 1, 1], torch.int32), indptr, B, (2, 2)), IndexError),
-        (lambda: fs.flagsparse_spmm_csr(data.to(torch.float16), indices, indptr, B.to(torch.float16), (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmm_csr(data.to(torch.int32), indices, indptr, B.to(torch.int32), (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmm_csr(data.to(torch.float16), indices, indptr, B, (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmm_csr_opt(data.to(torch.float16), indices, indptr, B.to(torch.float16), (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_csr(data, indices.to(torch.int16), indptr, B, (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_csr(data, indices, indptr.to(torch.int16), B, (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_csr_opt(data, indices, indptr, None, (2, 2)), ValueError),
@@ -108,7 +110,8 @@ def test_spmv_contract(tiny, cuda, fsb_lib):
         (lambda: fs.flagsparse_spmv_csr(data, t([0, 2, 1], torch.int32), indptr, x, (2, 2)), IndexError),
         (lambda: fs.flagsparse_spmv_csr(data, t([0, -1, 1], torch.int32), indptr, x, (2, 2)), IndexError),
         (lambda: fs.flagsparse_spmv_csr(data, indices.to(torch.int16), indptr, x, (2, 2)), TypeError),
-        (lambda: fs.flagsparse_spmv_csr(data.to(torch.bfloat16), indices, indptr, x.to(torch.bfloat16), (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmv_csr(data.to(torch.int64), indices, indptr, x.to(torch.int64), (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmv_csr(data.to(torch.bfloat16), indices, indptr, x, (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmv_csr(data, indices, indptr, x.to(torch.float64), (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmv_csr(data, indices, indptr, torch.ones(3, device=cuda), (2, 2)), ValueError),
         (lambda: fs.flagsparse_spmv_csr(data, indices, indptr, x.reshape(1, 2), (2, 2)), ValueError),

@@ -157,7 +157,8 @@ def test_coo_argument_contract(cuda, fsb_lib):
         (lambda: fs.flagsparse_spmm_coo(d, f([0, 2, 1], torch.int32), c, B, (2, 2)), IndexError),
         (lambda: fs.flagsparse_spmm_coo(d, r, f([0, 5, 0], torch.int32), B, (2, 2)), IndexError),
         (lambda: fs.flagsparse_spmm_coo(d, r, c, B.double(), (2, 2)), TypeError),
-        (lambda: fs.flagsparse_spmm_coo(d.half(), r, c, B.half(), (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmm_coo(d.half(), r, c, B, (2, 2)), TypeError),
+        (lambda: fs.flagsparse_spmm_coo(d.to(torch.int32), r, c, B.to(torch.int32), (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_coo(d, r.to(torch.int16), c, B, (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_coo(d, r, c.to(torch.int16), B, (2, 2)), TypeError),
         (lambda: fs.flagsparse_spmm_coo(d, r, c, B.cpu(), (2, 2)), ValueError),
