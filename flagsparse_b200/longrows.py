@@ -33,6 +33,7 @@ MIN_UNIT_ENTRIES = 4096
 UNIT_FIXED_BYTES = 48 * 1024  # added to the x chunk: cost of a unit in streamed-byte equivalents (CTA balancing)
 MIN_LONG_SHARE = 0.15       # of all entries: below this the split does not pay
 MIN_LONG_NNZ = 1 << 22
+MAX_CANDIDATE_NNZ = 1 << 29  # the regrouping sorts all candidate entries at once: beyond this it is not attempted
 ACC_CAP = None              # accumulators per group; None = what fits in shared memory (tests lower it)
 
 

@@ -197,7 +197,7 @@ def _split_long_rows(data, kernel_indices, kernel_indptr, n_rows, n_cols, shape,
     threshold = longrows.long_row_threshold()
     lens, candidates, cand_nnz = longrows.split_rows(kernel_indptr, n_rows, threshold or longrows.MIN_CANDIDATE_LEN)
     enough = lambda k: k >= longrows.MIN_LONG_NNZ and k >= longrows.MIN_LONG_SHARE * nnz  # noqa: E731
-    if not enough(cand_nnz):
+    if not enough(cand_nnz) or cand_nnz > longrows.MAX_CANDIDATE_NNZ:
         return None
     built = longrows.build_long_row_layout(data, kernel_indices, kernel_indptr, lens, candidates, n_cols,
                                            min_unit_entries=0 if threshold else longrows.MIN_UNIT_ENTRIES)
