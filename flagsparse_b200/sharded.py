@@ -181,7 +181,8 @@ class ShardedCsrSpmv:
                     _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
                     _ptr(p.data), _ptr(p.kernel_indices), p.kernel_indptr.data_ptr(), _ptr(x),
                     self._peer_ptrs.data_ptr(), self.world, base + self.row_start, p.n_rows, p.n_cols, p.data.numel(),
-                    self._peer_algo, p.tuning if self._peer_algo == _lib.FSB_SPMV_STREAM else 0, None if p.tile_row is None else p.tile_row.data_ptr(),
+                    self._peer_algo, p.tuning if self._peer_algo == _lib.FSB_SPMV_STREAM else 0,
+                    None if p.tile_row is None else p.tile_row.data_ptr(),
                     None if p.scratch is None else p.scratch.data_ptr(),
                     0 if p.scratch is None else p.scratch.numel(), _stream_ptr(self.device),
                 )

@@ -285,7 +285,8 @@ def _spmv_launch(prepared, x, y):
             longrows.launch_long_rows(layout, x, y, p.n_cols, _stream_ptr(dev))
         return
     algo = p.algo if p.tile_row is not None else _lib.FSB_SPMV_VECTOR
-    tuning = p.tuning if algo == _lib.FSB_SPMV_STREAM else (p.tuning & 0xFF if p.tuning & 0xFF in (2, 4, 8, 16, 32) else 0)
+    lanes = p.tuning & 0xFF
+    tuning = p.tuning if algo == _lib.FSB_SPMV_STREAM else (lanes if lanes in (2, 4, 8, 16, 32) else 0)
     with torch.cuda.device(dev):
         rc = L.fsb_spmv_csr(
             _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
