@@ -491,6 +491,9 @@ def run_ours(args, workload):
                     step1()
                 n1 = max(3, min(args.steps, 50))
                 t1 = timed_region(torch, step1, n1, lambda: None) / n1
+                extra["scaling_reference"] = ("strong scaling of this workload: divide by single_gpu_same_workload "
+                                              "(the same matrix on one GPU, timed by rank 0 in this run); the default "
+                                              "--gpus 1 run is another workload (c2)")
                 extra["single_gpu_same_workload"] = {"ms_per_step": t1 * 1e3, "value": nbytes / t1 / 1e9,
                                                      "unit": "GB/s", "kernel": prep1.opt_buckets[0]["kind"],
                                                      "steps": n1, "speedup_at_n_gpus": t1 / (elapsed / args.steps)}
