@@ -17,7 +17,11 @@ from ._common import _VTYPE
 SM_COUNT_FALLBACK = 148
 CTAS_PER_SM = 1              # one 1024-thread CTA (row block) per SM
 # the kernel is worth its second copy of the matrix only when the extra reads of x and the padding stay small
-MAX_X_OVERHEAD = 1.3        # bytes of x chunks loaded / bytes of entries streamed
+# bytes of x chunks loaded / bytes of entries streamed.  float32: measured on a band of +-2^20 columns (0.89: 319 G
+# entries/s against 231 G/s of the vector kernel; the SM's intake of about 37 GB/s is what bounds it, which puts the
+# break-even near 1.9).  float64 entries are 12 bytes and their chunks hold half the columns: estimate, not measured.
+MAX_X_OVERHEAD = 1.3
+MAX_X_OVERHEAD_F64 = 0.8
 MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
 N_BUFFERS = 2               # chunks of x in shared memory (fetched N_BUFFERS - 1 units ahead)
 MAX_RUN = 16                # entries of one row inside one unit = rounds per piece (see csrc/spmv_panel.cu)
@@ -239,7 +243,8 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     n_ch = -(-n_cols // CW)
     if not force:
         n_units = estimate_units(indices, indptr, n_rows, n_cols, RB, CW)
-        if n_units is None or n_units * CW * sv > MAX_X_OVERHEAD * nnz * (sv + 4):
+        limit = MAX_X_OVERHEAD if sv == 4 else MAX_X_OVERHEAD_F64
+        if n_units is None or n_units * CW * sv > limit * nnz * (sv + 4):
             return None
     vals, rcs, upieces, chunks, blocks = [], [], [], [], []
     piece_base = 0
