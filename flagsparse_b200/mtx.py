@@ -8,8 +8,8 @@ Same name, arguments and result as the loader the reference's benchmark scripts 
   * only the first `nnz` data lines count; entries outside the matrix are dropped;
   * entries that land on the same (row, column) are summed, in file order and in double precision;
   * columns come out sorted inside each row; column indices and the row pointer are int64.
-The reference walks the file entry by entry through Python dictionaries; this loader does the same arithmetic with
-numpy arrays (one stable sort), which reads SuiteSparse-sized files in seconds.  Complex files are refused: the
+The reference walks the file entry by entry through Python dictionaries; this loader parses the entries with
+numpy's text reader and does the same arithmetic with arrays (one stable sort).  Complex files are refused: the
 kernels here take float32 and float64 values.
 """
 
@@ -49,13 +49,33 @@ def _parse(file_path):
     is_pattern = field == "pattern"
     if field == "complex":
         raise TypeError(f"Matrix Market file {file_path} stores complex values; float32/float64 only here")
+    rows, cols, vals = _parse_entries(data_lines, is_pattern)
+    return field, symmetry, n_rows, n_cols, nnz, rows, cols, vals
+
+
+def _parse_entries(data_lines, is_pattern):
+    """0-based rows and columns and float64 values of the data lines.  numpy's text reader takes the regular case
+    (every line with the same number of fields); anything else goes line by line, which also finds the line to
+    name in an error."""
+    if not data_lines:
+        return np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.int64), np.zeros(0, dtype=np.float64)
+    try:
+        table = np.loadtxt(data_lines, dtype=np.float64, ndmin=2, comments=None)
+        if table.shape[0] == len(data_lines) and table.shape[1] >= (2 if is_pattern else 3):
+            rows = table[:, 0].astype(np.int64) - 1
+            cols = table[:, 1].astype(np.int64) - 1
+            vals = np.ones(len(data_lines), dtype=np.float64) if is_pattern else np.ascontiguousarray(table[:, 2])
+            if np.array_equal(rows + 1, table[:, 0]) and np.array_equal(cols + 1, table[:, 1]):
+                return rows, cols, vals
+    except ValueError:
+        pass
     rows = np.empty(len(data_lines), dtype=np.int64)
     cols = np.empty(len(data_lines), dtype=np.int64)
     vals = np.ones(len(data_lines), dtype=np.float64)
     for k, line in enumerate(data_lines):
         parts = line.split()
         if len(parts) < 2:
-            rows[k] = cols[k] = -1          # dropped below, like any entry outside the matrix
+            rows[k] = cols[k] = -1          # dropped later, like any entry outside the matrix
             continue
         rows[k] = int(parts[0]) - 1
         cols[k] = int(parts[1]) - 1
@@ -63,7 +83,7 @@ def _parse(file_path):
             if len(parts) < 3:
                 raise ValueError(f"Matrix Market entry is missing a numeric value: {line}")
             vals[k] = float(parts[2])
-    return field, symmetry, n_rows, n_cols, nnz, rows, cols, vals
+    return rows, cols, vals
 
 
 def mtx_to_csr_arrays(file_path):
