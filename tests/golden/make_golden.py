@@ -18,7 +18,9 @@ the reference's @triton.jit kernels:
 plus the pure host helpers (_resolve_spmm_alg1_launch_config, _select_spmm_opt_block_n,
 coo_to_csr_for_spmv), and the Matrix Market loader of the reference's benchmark scripts
   load_mtx_to_csr_torch  (tests/test_spmv.py:29-103 and tests/test_spmm.py:163-268 of the reference)
-on the small files of tests/golden/mtx/.  `--only coo` / `--only mtx` regenerate those fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
+on the small files of tests/golden/mtx/, and the base SpMV / SpMM paths on float16, bfloat16, complex64 and
+complex128 values (the same two launch helpers; the reference widens or takes real views there).
+`--only coo` / `--only mtx` / `--only wide` regenerate those fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
 synthetic generator changes.  Nothing here is imported by the package, the tests or the benchmark.
 """
 
@@ -192,6 +194,44 @@ def make_coo(index, V, MC):
         print("coo", name, val.size, index["coo"][name], flush=True)
 
 
+WIDE = {"f16": torch.float16, "bf16": torch.bfloat16, "c64": torch.complex64, "c128": torch.complex128}
+
+
+def _storable(t):
+    """numpy has no bfloat16: store it (and float16) widened to float32, which is exact."""
+    return t.to(torch.float32).numpy() if t.dtype in (torch.float16, torch.bfloat16) else t.numpy()
+
+
+def make_wide(index, R, M):
+    """Outputs of the reference's base SpMV and SpMM helpers for the four value types it widens or splits."""
+    index["wide"] = {}
+    lens = [0, 3, 17, 1, 0, 40, 5, 9, 64, 2, 0, 31]
+    _, indices, indptr = handmade_csr(41, lens, 96, np.float32, np.int32, np.int32)
+    n_rows, n_cols, nnz = len(lens), 96, int(indptr[-1])
+    rng = np.random.default_rng(42)
+    for tag, dt in WIDE.items():
+        def values(shape):
+            v = rng.uniform(-1, 1, shape)
+            if dt.is_complex:
+                v = v + 1j * rng.uniform(-1, 1, shape)
+            return torch.from_numpy(v).to(dt)
+        data, x, B = values(nnz), values(n_cols), values((n_cols, 6))
+        ti, tp = _t(indices), _t(indptr)
+        prepared = R.PreparedCsrSpmv(data=data, kernel_indices=ti, kernel_indptr=tp, shape=(n_rows, n_cols),
+                                     n_rows=n_rows, n_cols=n_cols, block_nnz=256, max_segments=1, max_row_nnz=max(lens),
+                                     opt_buckets=[])
+        y = R._triton_spmv_csr_impl_prepared(prepared, x)
+        launch = M._resolve_spmm_alg1_launch_config(6, max(lens))
+        C = M._triton_spmm_csr_impl(data, ti, tp.to(torch.int64), B, n_rows, 6, block_n=launch["block_n"],
+                                    block_nnz=launch["block_nnz"])
+        assert y.dtype == dt and C.dtype == dt
+        np.savez_compressed(os.path.join(HERE, f"wide_{tag}.npz"), data=_storable(data), indices=indices, indptr=indptr,
+                            shape=np.asarray((n_rows, n_cols)), x=_storable(x), B=_storable(B), y=_storable(y),
+                            C=_storable(C))
+        index["wide"][tag] = {"dtype": str(dt), "nnz": nnz}
+        print("wide", tag, index["wide"][tag], flush=True)
+
+
 def make_mtx(index, reference_root):
     """CSR arrays the reference's two loaders produce for tests/golden/mtx/*.mtx (float32 and float64, on CPU)."""
     import glob
@@ -243,7 +283,7 @@ def host_helper_goldens(R, M):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
-    ap.add_argument("--only", choices=("all", "coo", "mtx"), default="all")
+    ap.add_argument("--only", choices=("all", "coo", "mtx", "wide"), default="all")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from flagsparse.sparse_operations import spmm_coo as MC  # noqa: E402
@@ -252,11 +292,13 @@ def main():
     from flagsparse.sparse_operations import spmv_csr as R  # noqa: E402
 
     index_path = os.path.join(HERE, "index.json")
-    if args.only in ("coo", "mtx"):
+    if args.only in ("coo", "mtx", "wide"):
         with open(index_path) as f:
             index = json.load(f)
         if args.only == "coo":
             make_coo(index, V, MC)
+        elif args.only == "wide":
+            make_wide(index, R, M)
         else:
             make_mtx(index, args.reference)
         with open(index_path, "w") as f:
@@ -277,6 +319,7 @@ def main():
         print("spmm", name, data.size, meta, flush=True)
     make_coo(index, V, MC)
     make_mtx(index, args.reference)
+    make_wide(index, R, M)
     index["host"] = host_helper_goldens(R, M)
     with open(index_path, "w") as f:
         json.dump(index, f, indent=1, sort_keys=True)

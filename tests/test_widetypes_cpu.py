@@ -74,3 +74,41 @@ def test_native_types_are_not_split():
     assert W.compute_dtype(torch.complex128) == torch.float64 and W.compute_dtype(torch.bfloat16) == torch.float32
     with pytest.raises(ValueError):
         W.product("other", [], torch.ones(2), _launch, (2,), torch.float32)
+
+
+# ---- against outputs of the reference's own base paths (tests/golden/wide_*.npz) ----------------------------------
+GOLDEN_DTYPES = {"f16": torch.float16, "bf16": torch.bfloat16, "c64": torch.complex64, "c128": torch.complex128}
+# the reference rounds a float32 (or float64) sum to the caller's type as this package does; the sums themselves may
+# differ in their last bits (another order of additions), which can move the rounded result by one unit
+GOLDEN_TOL = {"f16": 2.0 ** -10, "bf16": 2.0 ** -7, "c64": 4e-6, "c128": 4e-15}
+
+
+def load_wide_golden(tag):
+    import os
+
+    from helpers import GOLDEN, load_golden
+
+    g = load_golden(os.path.join(GOLDEN, f"wide_{tag}.npz"))
+    dt = GOLDEN_DTYPES[tag]
+    for k in ("data", "x", "B", "y", "C"):
+        g[k] = torch.from_numpy(g[k]).to(dt)      # float16 / bfloat16 were stored widened to float32 (exact)
+    return g, dt
+
+
+@pytest.mark.parametrize("tag", sorted(GOLDEN_DTYPES))
+def test_arithmetic_against_reference_outputs(tag):
+    g, dt = load_wide_golden(tag)
+    kind, reals = W.split_values(g["data"])
+    parts = [sp.csr_matrix((r.numpy(), g["indices"], g["indptr"]), shape=g["shape"]) for r in reals]
+    wide = torch.complex128 if dt in W.COMPLEX_DTYPES else torch.float64
+    a = sp.csr_matrix((g["data"].to(wide).numpy(), g["indices"], g["indptr"]), shape=g["shape"])
+    for operand, ref_out in ((g["x"], g["y"]), (g["B"], g["C"])):
+        out_shape = (g["shape"][0],) + tuple(operand.shape[1:])
+        got = W.product(kind, parts, operand, _launch, out_shape, dt)
+        mag = np.asarray(abs(a) @ np.abs(operand.to(wide).numpy()))
+        err = np.abs(got.to(wide).numpy() - ref_out.to(wide).numpy())
+        assert got.dtype == ref_out.dtype and got.shape == ref_out.shape
+        assert np.all(err <= GOLDEN_TOL[tag] * mag + 1e-300), float((err / np.maximum(mag, 1e-300)).max())
+        # the reference's own output against the exact product of the stored values: same bound as ours gets
+        exact = np.asarray(a @ operand.to(wide).numpy())
+        assert np.all(np.abs(ref_out.to(wide).numpy() - exact) <= GOLDEN_TOL[tag] * mag + 1e-300)

@@ -123,3 +123,22 @@ def test_tiny_and_empty(cuda, fsb_lib):
     # the COO SpMV entry point stays float32 / float64, as in the reference
     with pytest.raises(TypeError):
         fs.flagsparse_spmv_coo(d, i, i, x, (3, 2))
+
+
+@pytest.mark.parametrize("tag", ["bf16", "c128", "c64", "f16"])
+def test_against_reference_outputs(cuda, fsb_lib, tag):
+    """The public entry points on the inputs of tests/golden/wide_*.npz against the outputs of the reference's own
+    base SpMV / SpMM helpers for these value types."""
+    from test_widetypes_cpu import GOLDEN_TOL, load_wide_golden
+
+    g, dt = load_wide_golden(tag)
+    wide = torch.complex128 if dt in W.COMPLEX_DTYPES else torch.float64
+    a = sp.csr_matrix((g["data"].to(wide).numpy(), g["indices"], g["indptr"]), shape=g["shape"])
+    d, i, p = g["data"].to(cuda), torch.from_numpy(g["indices"]).to(cuda), torch.from_numpy(g["indptr"]).to(cuda)
+    y = fs.flagsparse_spmv_csr(d, i, p, g["x"].to(cuda), g["shape"])
+    C = fs.flagsparse_spmm_csr(d, i, p.to(torch.int64), g["B"].to(cuda), g["shape"])
+    for got, ref_out, operand in ((y, g["y"], g["x"]), (C, g["C"], g["B"])):
+        mag = np.asarray(abs(a) @ np.abs(operand.to(wide).numpy()))
+        err = np.abs(got.cpu().to(wide).numpy() - ref_out.to(wide).numpy())
+        assert got.dtype == ref_out.dtype and tuple(got.shape) == tuple(ref_out.shape)
+        assert np.all(err <= GOLDEN_TOL[tag] * mag + 1e-300), float((err / np.maximum(mag, 1e-300)).max())
