@@ -8,7 +8,7 @@ row-major B.  Compute goes through libfsb.so (include/fsb.h); there is no Triton
 from ._common import SUPPORTED_INDEX_DTYPES, SUPPORTED_VALUE_DTYPES, _tolerance_for_dtype
 from .coo import PreparedCoo, flagsparse_spmm_coo, flagsparse_spmv_coo, prepare_spmv_coo
 from .mtx import load_mtx_to_csr_torch
-from .sharded import ShardedCsrSpmv, partition_rows_by_nnz
+from .sharded import ShardedCsrSpmm, ShardedCsrSpmv, partition_rows_by_nnz
 from .spmm_csr import (
     PreparedCsrSpmmOpt,
     flagsparse_spmm_csr,
@@ -43,5 +43,6 @@ __all__ = [
     "flagsparse_spmm_csr_opt",
     "load_mtx_to_csr_torch",
     "ShardedCsrSpmv",
+    "ShardedCsrSpmm",
     "partition_rows_by_nnz",
 ]

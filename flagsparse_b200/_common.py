@@ -87,3 +87,58 @@ def _tile_plan(indptr, n_rows, nnz, tile_nnz):
         )
     _lib.check(rc, "fsb_csr_tile_plan")
     return plan
+
+
+class StatusWord:
+    """The device word through which a kernel reports that one of its bounded waits ran out, and the host side of
+    it.  After each launch the word is copied to pinned host memory behind an event; the next call on the same
+    object (or an explicit check()) looks at the copy once the event has passed, resets the word and raises, so a
+    product whose kernel gave up is never handed on silently."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self._host = None
+        self._event = None
+        self._what = None
+
+    def data_ptr(self):
+        return self.word.data_ptr()
+
+    def item(self):
+        return int(self.word.item())
+
+    def posted(self, what, stream=None):
+        """Call right after a launch that may set the word; `stream` is the torch stream of that launch (default:
+        the current one)."""
+        if not self.word.is_cuda:
+            return
+        if self._host is None:
+            self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._event = torch.cuda.Event()
+        stream = stream or torch.cuda.current_stream(self.word.device)
+        with torch.cuda.stream(stream):
+            self._host.copy_(self.word, non_blocking=True)
+        self._event.record(stream)
+        self._what = what
+
+    def poll(self):
+        """Raise if an earlier launch is known to have failed; never waits for the GPU."""
+        if self._what is None or not self._event.query():
+            return
+        self._raise_if_set()
+
+    def check(self):
+        """Wait for the last launch and raise if it failed."""
+        if self._what is None:
+            return
+        self._event.synchronize()
+        self._raise_if_set()
+
+    def _raise_if_set(self):
+        what, code = self._what, int(self._host[0])
+        self._what = None
+        if code != 0:
+            self.word.zero_()
+            self._host.zero_()
+            raise RuntimeError(f"{what}: a device-side wait ran out (status {code}); the result of that call is "
+                               "incomplete")

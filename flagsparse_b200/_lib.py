@@ -41,18 +41,16 @@ SIGNATURES = {
     "fsb_spmv_csr": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp]),
     "fsb_spmv_csr_scatter": (
         _i32,
-        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp],
+        [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _sz, _vp],
     ),
     "fsb_spmv_csr_noalloc": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _vp, _vp]),
-    "fsb_spmv_panel_piece_slots": (_i32, []),
+    "fsb_spmv_panel_piece_slots": (_i32, [_i32]),
     "fsb_spmv_panel_smem_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "fsb_spmv_panel_static_smem_bytes": (_sz, []),
-    "fsb_spmv_csr_panel": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i64, _vp,
-                                  _vp]),
-    "fsb_spmv_csr_panel_scatter": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i64,
-                                          _i64, _i64, _vp, _vp]),
-    "fsb_spmv_csr_panel_groups": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
-                                         _i32, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "fsb_spmv_csr_panel": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
+                                  _i64, _i64, _vp, _vp]),
+    "fsb_spmv_csr_panel_groups": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp,
+                                         _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
     "fsb_spmm_csr_scratch_bytes": (_sz, [_i32, _i64, _i64]),
     "fsb_spmm_csr": (
         _i32,

@@ -42,12 +42,18 @@ struct PeerOut {
   V* const* peers;
   int n_peers;
   int64_t row_offset;
+  int first_peer;                          // this GPU's index: destinations are taken in an order rotated by it
+  // Destination visited k-th by this CTA.  Rotating by the GPU's own index and by the CTA keeps the GPUs (and the
+  // CTAs of one GPU) from all writing to the same destination at the same moment.
+  __device__ __forceinline__ int dest(int k) const {
+    return (int)(((unsigned)first_peer + 1u + blockIdx.x + (unsigned)k) % (unsigned)n_peers);
+  }
   __device__ __forceinline__ void store(int64_t i, V v) const {
-    for (int p = 0; p < n_peers; ++p) peers[p][row_offset + i] = v;
+    for (int k = 0; k < n_peers; ++k) peers[dest(k)][row_offset + i] = v;
   }
   __device__ __forceinline__ void store_block(int64_t row0, const V* src, int first, int last, int tid) const {
-    for (int p = 0; p < n_peers; ++p) {
-      V* dst = peers[p] + row_offset + row0;
+    for (int k = 0; k < n_peers; ++k) {
+      V* dst = peers[dest(k)] + row_offset + row0;
       for (int i = first + tid; i < last; i += kThreads) dst[i] = src[i];
     }
   }
@@ -460,7 +466,7 @@ struct SpmvArgs {
   const void *data, *idx, *ptr, *x;
   void* y;
   void* const* y_peers;
-  int n_peers;
+  int n_peers, first_peer;
   int64_t row_offset, n_rows, nnz;
   int algo, tuning;
   const int32_t* tile_row;
@@ -472,14 +478,14 @@ template <typename V, typename I, typename P>
 static int spmv_typed(const SpmvArgs& a) {
   if (a.algo == FSB_SPMV_VECTOR) {
     if (a.y_peers) {
-      PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset};
+      PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset, a.first_peer};
       return run_vector<V, I, P, PeerOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.n_rows, a.nnz, a.tuning & 0xff, a.st);
     }
     LocalOut<V> out{(V*)a.y};
     return run_vector<V, I, P, LocalOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.n_rows, a.nnz, a.tuning, a.st);
   }
   if (a.y_peers) {
-    PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset};
+    PeerOut<V> out{(V* const*)a.y_peers, a.n_peers, a.row_offset, a.first_peer};
     return run_stream<V, I, P, PeerOut<V>>(a.data, a.idx, a.ptr, a.x, out, a.tile_row, a.scratch, a.nnz,
                                            a.tuning, a.st);
   }
@@ -556,28 +562,30 @@ extern "C" int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, c
     if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
     if (!aligned_to(scratch, 16)) return FSB_EALIGN;
   }
-  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, n_rows, nnz, algo, tuning, tile_row, scratch, st};
+  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, 0, n_rows, nnz, algo, tuning, tile_row, scratch, st};
   return spmv_dispatch(vtype, itype, ptype, a);
 }
 
 extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
                                     const void* indptr, const void* x, void* const* y_peers, int n_peers,
-                                    int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int algo,
+                                    int first_peer, int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                                    int algo,
                                     int tuning, const int32_t* tile_row, void* scratch, size_t scratch_bytes,
                                     void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
   if (rc != FSB_OK) return rc;
   if (y_peers == nullptr || n_peers < 1 || n_peers > 64 || row_offset < 0) return FSB_EINVAL;
+  if (first_peer < 0 || first_peer >= n_peers) return FSB_EINVAL;
   if (n_rows == 0) return FSB_OK;
   if (nnz == 0) {
     const unsigned g = (unsigned)((n_rows + kThreads - 1) / kThreads);
     if (vtype == FSB_F32)
       fill_zero_kernel<float, PeerOut<float>><<<g, kThreads, 0, st>>>(
-          PeerOut<float>{(float* const*)y_peers, n_peers, row_offset}, n_rows);
+          PeerOut<float>{(float* const*)y_peers, n_peers, row_offset, first_peer}, n_rows);
     else
       fill_zero_kernel<double, PeerOut<double>><<<g, kThreads, 0, st>>>(
-          PeerOut<double>{(double* const*)y_peers, n_peers, row_offset}, n_rows);
+          PeerOut<double>{(double* const*)y_peers, n_peers, row_offset, first_peer}, n_rows);
     FSB_RETURN_IF_LAUNCH_FAILED();
     return FSB_OK;
   }
@@ -588,7 +596,7 @@ extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void*
     if (scratch_bytes < fsb_spmv_csr_scratch_bytes(vtype, nnz, tuning)) return FSB_ESCRATCH;
     if (!aligned_to(scratch, 16)) return FSB_EALIGN;
   }
-  SpmvArgs a{data, indices, indptr, x, nullptr, y_peers, n_peers, row_offset, n_rows, nnz,
+  SpmvArgs a{data, indices, indptr, x, nullptr, y_peers, n_peers, first_peer, row_offset, n_rows, nnz,
              algo, tuning, tile_row, scratch, st};
   return spmv_dispatch(vtype, itype, ptype, a);
 }
@@ -650,6 +658,6 @@ extern "C" int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void*
   void* scratch = nullptr;
   rc = noalloc_scratch_address(&scratch);
   if (rc != FSB_OK) return rc;
-  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, n_rows, nnz, FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
+  SpmvArgs a{data, indices, indptr, x, y, nullptr, 0, 0, 0, n_rows, nnz, FSB_SPMV_STREAM, tuning, tile_row, scratch, st};
   return spmv_dispatch(vtype, itype, ptype, a);
 }

@@ -6,19 +6,24 @@
 // towards L2, so the product runs at the speed of the gathers, not of HBM.  Shared memory serves 32
 // scattered 4-byte reads per clock.  The prepare step therefore regroups the entries (once per matrix)
 // into units = (block of RB consecutive rows) x (chunk of CW consecutive columns); inside a unit the
-// entries keep their row-major order and are cut into pieces of 512 slots such that the entries of one
-// row never straddle two pieces (unused slots hold a sentinel).  An entry is a value plus one packed word
-// (local row << 16 | buffer parity * CW + local column): 8 bytes for float32, the same as CSR with 32-bit
-// indices.  One CTA owns one row block:
+// entries keep their row-major order and are cut into pieces of 32 * R slots (R = 4, 8 or 16, fixed per
+// layout) such that the entries of one row never straddle two pieces (unused slots hold a sentinel).
+// An entry is a value plus one packed word (local row << 16 | x buffer * CW + local column): 8 bytes for
+// float32, the same as CSR with 32-bit indices.  One CTA owns one row block:
 //   - the CW elements of x a unit needs arrive in shared memory by a cp.async.bulk copy (mbarrier
-//     completion), double-buffered so that the next unit's chunk is in flight while this one is used;
-//   - a warp takes a whole piece: lane l owns slots 16l .. 16l+15 (stored interleaved so that each 128-bit
-//     load of the warp is contiguous).  In round k every lane handles its k-th slot.  Two slots of one round are at least 16 positions apart,
-//     and a row has at most 16 entries in a unit (the prepare step refuses the matrix otherwise), so the
-//     32 lanes of a round always touch 32 different rows: each lane simply adds value * x[column] to its
-//     row's accumulator in shared memory, with no shuffles and no atomics.  Rounds follow each other in
-//     program order, a row lives in one piece per unit, and units are separated by a CTA barrier, so
-//     every accumulator receives its terms in one fixed order: the result is bit-reproducible;
+//     completion), n_buffers - 1 units ahead of their use;
+//   - a warp takes a whole piece: lane l owns slots R*l .. R*l+R-1 (stored interleaved so that each 128-bit
+//     load of the warp is contiguous).  In round k every lane handles its k-th slot and keeps the running sum
+//     of its current row in a register; when the row ends it adds the sum to the row's accumulator in shared
+//     memory.  A row with at most R entries in the unit touches at most two lanes and ends in them in
+//     different rounds, so the 32 lanes of a round always add into 32 different accumulators: no shuffles, no
+//     atomics.  Layouts that hold longer runs say so (FSB_PANEL_LONG_RUNS); for them the add of a lane's last
+//     slot goes through a segmented warp reduction whenever two neighbouring lanes end on the same row;
+//   - the pieces of the CTA are dealt to its warps round-robin across unit boundaries, and every warp keeps
+//     the next few 4-slot groups of its own pieces in flight (a register ring), whichever unit they belong
+//     to: a unit with only a few pieces costs no trip to DRAM of its own;
+//   - rounds follow each other in program order, a row lives in one piece per unit, and units are separated
+//     by a CTA barrier, so every accumulator receives its terms in one fixed order: bit-reproducible;
 //   - after the last unit the accumulators are written to y, each row exactly once.
 #include "fsb_common.cuh"
 
@@ -26,9 +31,8 @@ namespace fsb {
 
 constexpr int kPanelWarps = 32;
 constexpr int kPanelThreads = kPanelWarps * 32;
-constexpr int kPieceSlots = 512;   // 32 lanes x 16 rounds
-constexpr int kPieceRounds = 16;
 constexpr int kPanelWaitSpins = 1 << 22;
+constexpr int kPanelWaitSpinsDebug = 1 << 10;   // FSB_PANEL_DEBUG_TIMEOUT: give up quickly
 constexpr uint32_t kNoRow = 0xFFFFu;
 
 __device__ __forceinline__ uint32_t p_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -49,60 +53,82 @@ __device__ __forceinline__ bool p_try_wait(uint64_t* bar, uint32_t phase) {
                : "=r"(ok) : "r"(p_smem_addr(bar)), "r"(phase) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool p_wait_bounded(uint64_t* bar, uint32_t phase) {
-  for (int i = 0; i < kPanelWaitSpins; ++i)
+__device__ __forceinline__ bool p_wait_bounded(uint64_t* bar, uint32_t phase, int spins) {
+  for (int i = 0; i < spins; ++i)
     if (p_try_wait(bar, phase)) return true;
   return false;
 }
 
-// G consecutive slots of one lane (rounds k0 .. k0+G-1 of the piece).  Products of one row are summed in a
-// register and added to the row's accumulator when the row ends (next_row is the row of the lane's next slot,
-// or kNoRow after its last one).  Within one round the 32 lanes are on 32 different rows; a row that spans two
-// lanes ends in the first of them at its last slot and in the second one earlier, i.e. in different rounds.
-template <typename V, int G>
-__device__ __forceinline__ void panel_rounds(const V (&v)[G], const uint32_t (&w)[G], uint32_t next_word, V& acc,
-                                             const V* __restrict__ xs, V* __restrict__ y_part, uint32_t col_mask) {
-  // x does not change during a unit: all G gathers go out first, so that their latencies overlap instead of
+// Four consecutive slots of one lane: rounds 4g .. 4g+3 of a piece.
+template <typename V>
+struct Group {
+  V v[4];
+  uint32_t w[4];
+};
+
+// Storage inside a piece of 32 * R slots: slot (lane, k), k = 0..R-1, of the value array sits at
+// (k / E) * 32 * E + lane * E + k % E with E = elements per 16 bytes, and of the packed-word array at
+// (k / 4) * 128 + lane * 4 + k % 4, so that every 128-bit load of a warp reads 512 contiguous bytes.
+__device__ __forceinline__ void ld_group(const float* piece_val, const uint32_t* piece_rc, int lane, int g,
+                                         Group<float>& out) {
+  ld_stream4(piece_val + g * 128 + lane * 4, out.v);
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece_rc + g * 128 + lane * 4));
+  out.w[0] = t.x; out.w[1] = t.y; out.w[2] = t.z; out.w[3] = t.w;
+}
+__device__ __forceinline__ void ld_group(const double* piece_val, const uint32_t* piece_rc, int lane, int g,
+                                         Group<double>& out) {
+  const double2 a = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * g) * 64 + lane * 2));
+  const double2 b = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * g + 1) * 64 + lane * 2));
+  out.v[0] = a.x; out.v[1] = a.y; out.v[2] = b.x; out.v[3] = b.y;
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece_rc + g * 128 + lane * 4));
+  out.w[0] = t.x; out.w[1] = t.y; out.w[2] = t.z; out.w[3] = t.w;
+}
+
+// The four rounds of one group.  Products of one row are summed in a register and added to the row's
+// accumulator when the row ends (next_word is the lane's next slot, or a kNoRow word after its last one).
+//   LAST   this is the lane's last group of the piece: its fourth slot closes whatever row is open (a constant
+//          once the caller's loops are unrolled)
+//   CHECK  the layout may hold rows with more than R entries in a unit: such a row covers whole lanes, which
+//          all close it with their last slot, i.e. in the same round; those sums are combined by a segmented
+//          scan over the lanes (fixed order) and added once
+template <typename V, bool CHECK>
+__device__ __forceinline__ void panel_rounds4(const Group<V>& G, uint32_t next_word, const bool LAST, V& acc,
+                                              const V* __restrict__ xs, V* __restrict__ y_part, int lane) {
+  // x does not change during a unit: the gathers go out first, so that their latencies overlap instead of
   // queueing behind the per-round ordering points below
-  V p[G];
+  V p[4];
 #pragma unroll
-  for (int k = 0; k < G; ++k) p[k] = v[k] * xs[w[k] & col_mask];   // padding slots: value 0, column 0
+  for (int k = 0; k < 4; ++k) p[k] = G.v[k] * xs[G.w[k] & 0xFFFFu];   // padding slots: value 0, column 0
 #pragma unroll
-  for (int k = 0; k < G; ++k) {
-    const uint32_t row = w[k] >> 16;
-    const uint32_t next_row = (k + 1 < G ? w[k + 1] : next_word) >> 16;
+  for (int k = 0; k < 4; ++k) {
+    const uint32_t row = G.w[k] >> 16;
+    const uint32_t next_row = (k < 3 ? G.w[k + 1] : next_word) >> 16;
     const bool live = row != kNoRow;
     if (live) acc += p[k];
-    if (live && next_row != row) {
+    const bool flush = live && next_row != row;
+    if (CHECK && LAST && k == 3) {
+      const uint32_t row_up = __shfl_down_sync(0xffffffffu, row, 1);
+      const bool clash = flush && lane < 31 && row_up == row;
+      if (__any_sync(0xffffffffu, clash)) {
+        // inclusive segmented sum over the lanes that close the same row, then the last of them adds it
+        V s = flush ? acc : (V)0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const V t = __shfl_up_sync(0xffffffffu, s, o);
+          const uint32_t r = __shfl_up_sync(0xffffffffu, row, o);
+          if (lane >= o && r == row) s += t;
+        }
+        if (flush && (lane == 31 || row_up != row)) y_part[row] += s;
+        acc = (V)0;
+      } else if (flush) {
+        y_part[row] += acc;
+        acc = (V)0;
+      }
+    } else if (flush) {
       y_part[row] += acc;
       acc = (V)0;
     }
     __syncwarp();  // orders this round's accumulator updates before the next round's
-  }
-}
-
-// Storage inside a piece: slot (lane, k), k = 0..15, of the value array sits at (k / E) * 32 * E + lane * E + k % E
-// with E = elements per 16 bytes, and of the packed-word array at (k / 4) * 128 + lane * 4 + k % 4, so that every
-// 128-bit load of a warp reads 512 contiguous bytes.
-template <int G>
-__device__ __forceinline__ void ld_group(const float* piece, int lane, int g, float (&v)[G]) {
-  static_assert(G == 8, "float32 groups hold eight slots");
-  ld_stream4(piece + (2 * g) * 128 + lane * 4, *reinterpret_cast<float(*)[4]>(&v[0]));
-  ld_stream4(piece + (2 * g + 1) * 128 + lane * 4, *reinterpret_cast<float(*)[4]>(&v[4]));
-}
-template <int G>
-__device__ __forceinline__ void ld_group(const double* piece, int lane, int g, double (&v)[G]) {
-  static_assert(G == 4, "float64 groups hold four slots");
-  const double2 a = __ldcs(reinterpret_cast<const double2*>(piece + (2 * g) * 64 + lane * 2));
-  const double2 b = __ldcs(reinterpret_cast<const double2*>(piece + (2 * g + 1) * 64 + lane * 2));
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-template <int G>
-__device__ __forceinline__ void ld_words(const uint32_t* piece, int lane, int g, uint32_t (&w)[G]) {
-#pragma unroll
-  for (int q = 0; q < G / 4; ++q) {
-    const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece + (g * (G / 4) + q) * 128 + lane * 4));
-    w[4 * q] = t.x; w[4 * q + 1] = t.y; w[4 * q + 2] = t.z; w[4 * q + 3] = t.w;
   }
 }
 
@@ -121,60 +147,75 @@ struct PanelShared {
   int32_t* uch;   // unit_chunk of the window and of the next few units (kUnitWindow + kUnitLookahead)
 };
 
+struct PanelGeom {
+  int64_t n_cols;
+  int chunk_cols;
+  int n_buf;
+  int debug;      // FSB_PANEL_DEBUG_TIMEOUT: the first chunk's barrier expects bytes that never come
+};
+
 // Units u0 .. u1-1 of one CTA, in order: chunk of x in, pieces added into y_part.  Returns false when a bounded
 // wait ran out (every thread of the CTA gets the same answer).
 //   - x chunks are fetched n_buf - 1 units ahead into n_buf buffers (unit number `ord` of the CTA uses buffer
 //     ord % n_buf; the packed word of a slot already holds buffer * chunk_cols + local column);
-//   - the pieces of the CTA are dealt to its warps round-robin ACROSS units (piece p goes to warp
-//     (p - first piece of the CTA) % 32), and a warp fetches the first entries of its next piece while it works
-//     on the current one, whichever unit that piece belongs to: a unit with only a few pieces costs neither a
-//     trip to DRAM for its entries nor one for its tables.
-template <typename V>
+//   - piece p goes to warp (p - first piece of the CTA) % 32; the warp's groups form one stream q = 0, 1, ...
+//     (group q % (R/4) of its piece number q / (R/4)) of which D are held in a register ring: group q + D is
+//     requested as soon as group q has been consumed.
+template <typename V, int R, int D, bool CHECK>
 __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const uint32_t* __restrict__ rc,
                                                 const int32_t* __restrict__ unit_piece_ptr,
                                                 const int32_t* __restrict__ unit_chunk, int u0, int u1,
-                                                const V* __restrict__ x, int64_t n_cols, int chunk_cols, int n_buf,
+                                                const V* __restrict__ x, const PanelGeom& gm,
                                                 const PanelShared<V>& sh) {
+  constexpr int GPP = R / 4;          // groups per piece
+  constexpr int SLOTS = 32 * R;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk_cols = gm.chunk_cols, n_buf = gm.n_buf;
+  const int spins = gm.debug ? kPanelWaitSpinsDebug : kPanelWaitSpins;
   V* xs = sh.xs;
   V* y_part = sh.y_part;
   uint64_t* bars = sh.bars;
-  const uint32_t col_mask = (uint32_t)(n_buf * chunk_cols - 1);
-  const int buf_mask = n_buf - 1;
   if (u0 >= u1) return true;
 
   // chunk `c` of x into buffer `b`: bulk copy when the byte count is a multiple of 16, else plain loads
-  auto load_chunk = [&](int c, int b) {
+  auto load_chunk = [&](int c, int b, bool first) {
     const int64_t c0 = (int64_t)c * chunk_cols;
-    const int n = (int)((n_cols - c0) < (int64_t)chunk_cols ? (n_cols - c0) : (int64_t)chunk_cols);
+    const int n = (int)((gm.n_cols - c0) < (int64_t)chunk_cols ? (gm.n_cols - c0) : (int64_t)chunk_cols);
     const uint32_t bytes = (uint32_t)(n * sizeof(V));
     if ((bytes & 15u) == 0 && aligned_to_dev(x + c0)) {
       if (tid == 0) {
-        p_expect_tx(&bars[b], bytes);
+        p_expect_tx(&bars[b], bytes + ((first && gm.debug) ? 16u : 0u));
         p_bulk_g2s(xs + (size_t)b * chunk_cols, x + c0, bytes, &bars[b]);
       }
       return false;
     }
     for (int i = tid; i < n; i += kPanelThreads) xs[(size_t)b * chunk_cols + i] = __ldg(x + c0 + i);
-    if (tid == 0) p_expect_tx(&bars[b], 0);  // the phase completes as soon as this arrival lands
+    if (tid == 0) p_expect_tx(&bars[b], (first && gm.debug) ? 16u : 0u);  // completes as soon as this arrival lands
     return true;
   };
 
-  constexpr int G = sizeof(V) == 4 ? 8 : 4;   // slots per load group
-  constexpr int NG = kPieceRounds / G;        // groups per piece
+  const int p_first = unit_piece_ptr[u0];
   const int p_cta_end = unit_piece_ptr[u1];
-  int pc = unit_piece_ptr[u0] + warp;         // this warp's next piece
-  // the entries do not depend on x: the first group of the warp's first piece is fetched before anything else
-  V v[G];
-  uint32_t w[G];
-  if (pc < p_cta_end) {
-    ld_group<G>(val + (size_t)pc * kPieceSlots, lane, 0, v);
-    ld_words<G>(rc + (size_t)pc * kPieceSlots, lane, 0, w);
-  }
+  const int n_my = (p_cta_end - p_first - warp + kPanelWarps - 1) / kPanelWarps;   // pieces of this warp (may be <= 0)
+  const int n_groups = n_my > 0 ? n_my * GPP : 0;
+  Group<V> ring[D];
+  auto request = [&](int q, Group<V>& slot) {
+    if (q < n_groups) {
+      const size_t piece = (size_t)(p_first + warp + kPanelWarps * (q / GPP));
+      ld_group(val + piece * SLOTS, rc + piece * SLOTS, lane, q % GPP, slot);
+    }
+  };
+  // the entries do not depend on x: the first D groups of the warp are requested before anything else
+#pragma unroll
+  for (int i = 0; i < D; ++i) request(i, ring[i]);
+  int q = 0, phase = 0;
+  int pc = p_first + warp;            // this warp's next piece
+
   // chunks of the first n_buf - 1 units
   bool plain = false;  // some chunk was written with ordinary stores: needs a CTA barrier before its first use
-  for (int a = 0; a < n_buf - 1 && u0 + a < u1; ++a) plain |= load_chunk(unit_chunk[u0 + a], a);
+  for (int a = 0; a < n_buf - 1 && u0 + a < u1; ++a) plain |= load_chunk(unit_chunk[u0 + a], a, a == 0);
 
+  int b = 0, par = 0;                  // buffer and barrier parity of the current unit
   for (int w0 = u0; w0 < u1; w0 += kUnitWindow) {
     const int nwin = (u1 - w0) < kUnitWindow ? (u1 - w0) : kUnitWindow;
     const int nch = (u1 - w0) < (kUnitWindow + kUnitLookahead) ? (u1 - w0) : (kUnitWindow + kUnitLookahead);
@@ -183,37 +224,44 @@ __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const
     for (int i = tid; i < nch; i += kPanelThreads) sh.uch[i] = unit_chunk[w0 + i];
     __syncthreads();
     for (int u = w0; u < w0 + nwin; ++u) {
-      const int ord = u - u0, b = ord & buf_mask;
       // the buffer of the previous unit was last read before the barrier that closed it: free to refill
-      if (u + n_buf - 1 < u1) plain |= load_chunk(sh.uch[u + n_buf - 1 - w0], (ord + n_buf - 1) & buf_mask);
+      if (u + n_buf - 1 < u1) {
+        int bn = b + n_buf - 1;
+        bn = bn >= n_buf ? bn - n_buf : bn;
+        plain |= load_chunk(sh.uch[u + n_buf - 1 - w0], bn, u == u0 && n_buf == 1);
+      }
       const int p_end = sh.upp[u - w0 + 1];
-      if (!p_wait_bounded(&bars[b], (uint32_t)((ord / n_buf) & 1))) *sh.failed = 1;
-      if (plain && ord == 0) __syncthreads();  // later plain chunks are written at least one unit (barrier) ahead
+      if (!p_wait_bounded(&bars[b], (uint32_t)par, spins)) *sh.failed = 1;
+      if (plain && u == u0) __syncthreads();  // later plain chunks are written at least one unit (barrier) ahead
       while (pc < p_end) {
         V acc = (V)0;
 #pragma unroll
-        for (int g = 0; g < NG; ++g) {
-          // next group (of this piece, or the first one of this warp's next piece) in flight while this one is used
-          V v2[G];
-          uint32_t w2[G];
-          const bool more = g + 1 < NG;
-          const int np = more ? pc : pc + kPanelWarps;
-          const bool have = np < p_cta_end;
-          if (have) {
-            ld_group<G>(val + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, v2);
-            ld_words<G>(rc + (size_t)np * kPieceSlots, lane, more ? g + 1 : 0, w2);
-          }
-          const uint32_t next_word = more ? w2[0] : (kNoRow << 16);  // a lane's run ends with its last slot
-          panel_rounds<V, G>(v, w, next_word, acc, xs, y_part, col_mask);
-          if (have) {
+        for (int g = 0; g < GPP; ++g) {
 #pragma unroll
-            for (int k = 0; k < G; ++k) { v[k] = v2[k]; w[k] = w2[k]; }
+          for (int i = 0; i < D; ++i) {
+            if (phase == i) {
+              // a lane's run ends with its last slot of the piece; inside the piece the next group tells
+              const uint32_t next_word = (g + 1 < GPP) ? ring[(i + 1) % D].w[0] : (kNoRow << 16);
+              panel_rounds4<V, CHECK>(ring[i], next_word, g + 1 == GPP, acc, xs, y_part, lane);
+              request(q + D, ring[i]);
+            }
           }
+          phase = (phase + 1 == D) ? 0 : phase + 1;
+          ++q;
         }
         pc += kPanelWarps;
       }
       __syncthreads();  // every add of this unit is done; its x buffer may be refilled
-      if (*sh.failed) return false;
+      if (*sh.failed) {
+        // leave no copy in flight into this CTA's shared memory: one more bounded wait per chunk requested ahead
+        int bb = b, pp = par;
+        for (int a = 1; a < n_buf && u + a < u1; ++a) {
+          if (++bb == n_buf) { bb = 0; pp ^= 1; }
+          p_wait_bounded(&bars[bb], (uint32_t)pp, spins);
+        }
+        return false;
+      }
+      if (++b == n_buf) { b = 0; par ^= 1; }
     }
   }
   return true;
@@ -245,36 +293,38 @@ __device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* s
   __syncthreads();
 }
 
-// One CTA per block of rb_rows consecutive rows; every row of y is written exactly once (to y, or, when y_peers
-// is given, to y_peers[p][row_offset + row] for every p).
-template <typename V>
+// One CTA per block of rb_rows consecutive rows (block block_begin + blockIdx.x); every row of y the launch
+// covers is written exactly once.
+template <typename V, int R, int D, bool CHECK>
 __global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
                   const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
-                  const V* __restrict__ x, V* __restrict__ y, V* const* __restrict__ y_peers, int n_peers,
-                  int64_t row_offset, int64_t n_rows, int64_t n_cols, int rb_rows, int chunk_cols, int n_buf,
-                  int32_t* __restrict__ status) {
+                  const V* __restrict__ x, V* __restrict__ y, int block_begin, int64_t n_rows, int rb_rows,
+                  PanelGeom gm, int32_t* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char p_smem[];
   __shared__ __align__(8) PanelStatic p_static;
   const int tid = threadIdx.x;
-  const int rb = blockIdx.x;
+  const int rb = block_begin + (int)blockIdx.x;
   const int64_t r0 = (int64_t)rb * rb_rows;
   const int nr = (int)((n_rows - r0) < (int64_t)rb_rows ? (n_rows - r0) : (int64_t)rb_rows);
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, &p_static, chunk_cols, n_buf, nr);
-  if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x, n_cols,
-                          chunk_cols, n_buf, sh)) {
+  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, nr);
+  if (!panel_run_units<V, R, D, CHECK>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x,
+                                       gm, sh)) {
     if (tid == 0 && status != nullptr) atomicExch(status, 2);
     return;
   }
-  if (y_peers == nullptr) {
-    for (int i = tid; i < nr; i += kPanelThreads) y[r0 + i] = sh.y_part[i];
+  // the accumulators start on a 16-byte boundary of shared memory; so does y + r0 when rb_rows is a multiple of 4
+  V* dst = y + r0;
+  constexpr int E = 16 / (int)sizeof(V);
+  if (aligned_to_dev(dst)) {
+    const int nv = nr / E;
+    const float4* src4 = reinterpret_cast<const float4*>(sh.y_part);
+    float4* dst4 = reinterpret_cast<float4*>(dst);
+    for (int i = tid; i < nv; i += kPanelThreads) dst4[i] = src4[i];
+    for (int i = nv * E + tid; i < nr; i += kPanelThreads) dst[i] = sh.y_part[i];
   } else {
-    // sharded product: this GPU's rows go straight into every GPU's copy of y (coalesced stores over NVLink)
-    for (int p = 0; p < n_peers; ++p) {
-      V* dst = y_peers[p] + row_offset + r0;
-      for (int i = tid; i < nr; i += kPanelThreads) dst[i] = sh.y_part[i];
-    }
+    for (int i = tid; i < nr; i += kPanelThreads) dst[i] = sh.y_part[i];
   }
 }
 
@@ -285,14 +335,14 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
 // unit" still holds).  The units of a group are dealt to several CTAs by column range, so a CTA ends with
 // partial sums of its group's rows: it writes them to part[cta_part_ptr[cta] + (q - first q of the group)],
 // and panel_group_reduce_kernel adds the partial sums of each row in CTA order.
-template <typename V>
+template <typename V, int R, int D, bool CHECK>
 __global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc,
                          const int32_t* __restrict__ unit_piece_ptr, const int32_t* __restrict__ unit_chunk,
                          const int32_t* __restrict__ cta_unit_ptr, const int32_t* __restrict__ cta_group,
                          const int32_t* __restrict__ group_q_ptr, const int32_t* __restrict__ vbase,
                          const int64_t* __restrict__ cta_part_ptr, V* __restrict__ part, const V* __restrict__ x,
-                         int64_t n_cols, int chunk_cols, int n_buf, int32_t* __restrict__ status) {
+                         PanelGeom gm, int32_t* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char p_smem[];
   __shared__ __align__(8) PanelStatic p_static;
   const int tid = threadIdx.x;
@@ -302,9 +352,9 @@ spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__
   const int vb0 = vbase[q0];
   const int n_acc = vbase[q1] - vb0;
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, &p_static, chunk_cols, n_buf, n_acc);
-  if (!panel_run_units<V>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1], x, n_cols,
-                          chunk_cols, n_buf, sh)) {
+  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, n_acc);
+  if (!panel_run_units<V, R, D, CHECK>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1],
+                                       x, gm, sh)) {
     if (tid == 0 && status != nullptr) atomicExch(status, 2);
     return;
   }
@@ -333,11 +383,17 @@ panel_group_reduce_kernel(const V* __restrict__ part, const int32_t* __restrict_
   y[long_rows[q]] = (V)s;
 }
 
+// groups of a warp held in flight: as many as the register file allows with 1024 threads per CTA
+template <typename V> struct Depth { static constexpr int value = 4; };
+template <> struct Depth<double> { static constexpr int value = 2; };
+
 }  // namespace fsb
 
 using namespace fsb;
 
-extern "C" int fsb_spmv_panel_piece_slots(void) { return kPieceSlots; }
+extern "C" int fsb_spmv_panel_piece_slots(int rounds) {
+  return (rounds == 4 || rounds == 8 || rounds == 16) ? 32 * rounds : 0;
+}
 
 extern "C" size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers) {
   const size_t sv = vtype == FSB_F32 ? 4 : 8;
@@ -347,64 +403,66 @@ extern "C" size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_co
 extern "C" size_t fsb_spmv_panel_static_smem_bytes(void) { return sizeof(PanelStatic); }
 
 static bool panel_buffers_ok(int n_buffers, int chunk_cols) {
-  return (n_buffers == 2 || n_buffers == 4 || n_buffers == 8) && (int64_t)n_buffers * chunk_cols <= 65536;
+  return n_buffers >= 2 && n_buffers <= kMaxXBuffers && (int64_t)n_buffers * chunk_cols <= 65536;
 }
 
-static int panel_launch(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
-                        const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks, int32_t rb_rows,
-                        int32_t chunk_cols, int32_t n_buffers, const void* x, void* y, void* const* y_peers,
-                        int n_peers, int64_t row_offset, int64_t n_rows, int64_t n_cols, int32_t* status,
-                        void* stream_) {
+// FN<V, R, D, CHECK> for the runtime (vtype, rounds, long-runs flag)
+#define FSB_PANEL_DISPATCH(FN, V, LAUNCH)                                              \
+  do {                                                                                 \
+    constexpr int D_ = Depth<V>::value;                                                \
+    if (rounds == 4) {                                                                 \
+      if (check) LAUNCH((FN<V, 4, D_, true>)); else LAUNCH((FN<V, 4, D_, false>));     \
+    } else if (rounds == 8) {                                                          \
+      if (check) LAUNCH((FN<V, 8, D_, true>)); else LAUNCH((FN<V, 8, D_, false>));     \
+    } else {                                                                           \
+      if (check) LAUNCH((FN<V, 16, D_, true>)); else LAUNCH((FN<V, 16, D_, false>));   \
+    }                                                                                  \
+  } while (0)
+
+extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
+                                  const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
+                                  int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, int32_t rounds,
+                                  int32_t flags, int32_t block_begin, int32_t block_end, const void* x, void* y,
+                                  int64_t n_rows, int64_t n_cols, int32_t* status, void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
   if (n_rows < 0 || n_cols < 0 || n_row_blocks < 0 || rb_rows <= 0 || rb_rows >= 65535) return FSB_EINVAL;
   if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
   if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
-  if (n_rows == 0) return FSB_OK;
+  if (fsb_spmv_panel_piece_slots(rounds) == 0) return FSB_EINVAL;
+  if (block_begin < 0 || block_end > n_row_blocks || block_begin > block_end) return FSB_EINVAL;
+  if (n_rows == 0 || block_begin == block_end) return FSB_OK;
   if ((int64_t)n_row_blocks * rb_rows < n_rows) return FSB_EINVAL;
-  if (!val || !rc || !unit_piece_ptr || !unit_chunk || !rb_unit_ptr || !x || (!y && !y_peers)) return FSB_EINVAL;
+  if (!val || !rc || !unit_piece_ptr || !unit_chunk || !rb_unit_ptr || !x || !y) return FSB_EINVAL;
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
-#define FSB_PANEL_LAUNCH(V)                                                                                   \
-  do {                                                                                                        \
-    cudaError_t e = cudaFuncSetAttribute(spmv_panel_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                          \
-    if (e != cudaSuccess) return cuda_rc(e);                                                                  \
-    spmv_panel_kernel<V><<<(unsigned)n_row_blocks, kPanelThreads, smem, st>>>(                                \
-        (const V*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, (const V*)x, (V*)y, (V* const*)y_peers,   \
-        n_peers, row_offset, n_rows, n_cols, rb_rows, chunk_cols, n_buffers, status);                         \
+  const bool check = (flags & FSB_PANEL_LONG_RUNS) != 0;
+  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0};
+  const unsigned grid = (unsigned)(block_end - block_begin);
+#define FSB_PANEL_LAUNCH_(K)                                                                                    \
+  do {                                                                                                          \
+    cudaError_t e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+    if (e != cudaSuccess) return cuda_rc(e);                                                                    \
+    K<<<grid, kPanelThreads, smem, st>>>((const VT_*)val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr,          \
+                                         (const VT_*)x, (VT_*)y, block_begin, n_rows, rb_rows, gm, status);     \
   } while (0)
-  if (vtype == FSB_F32) FSB_PANEL_LAUNCH(float); else FSB_PANEL_LAUNCH(double);
-#undef FSB_PANEL_LAUNCH
+  if (vtype == FSB_F32) {
+    typedef float VT_;
+    FSB_PANEL_DISPATCH(spmv_panel_kernel, float, FSB_PANEL_LAUNCH_);
+  } else {
+    typedef double VT_;
+    FSB_PANEL_DISPATCH(spmv_panel_kernel, double, FSB_PANEL_LAUNCH_);
+  }
+#undef FSB_PANEL_LAUNCH_
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }
 
-extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
-                                  const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
-                                  int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x, void* y,
-                                  int64_t n_rows, int64_t n_cols, int32_t* status, void* stream_) {
-  if (y == nullptr && n_rows > 0) return FSB_EINVAL;
-  return panel_launch(vtype, val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, n_row_blocks, rb_rows, chunk_cols,
-                      n_buffers, x, y, nullptr, 0, 0, n_rows, n_cols, status, stream_);
-}
-
-extern "C" int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc,
-                                          const int32_t* unit_piece_ptr, const int32_t* unit_chunk,
-                                          const int32_t* rb_unit_ptr, int32_t n_row_blocks, int32_t rb_rows,
-                                          int32_t chunk_cols, int32_t n_buffers, const void* x, void* const* y_peers,
-                                          int n_peers, int64_t row_offset, int64_t n_rows, int64_t n_cols,
-                                          int32_t* status, void* stream_) {
-  if (y_peers == nullptr || n_peers < 1 || n_peers > 64 || row_offset < 0) return FSB_EINVAL;
-  return panel_launch(vtype, val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, n_row_blocks, rb_rows, chunk_cols,
-                      n_buffers, x, nullptr, y_peers, n_peers, row_offset, n_rows, n_cols, status, stream_);
-}
-
 extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                                          const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
-                                         int32_t chunk_cols, int32_t n_buffers, int32_t max_group_acc,
-                                         const int32_t* cta_group,
+                                         int32_t chunk_cols, int32_t n_buffers, int32_t rounds, int32_t flags,
+                                         int32_t max_group_acc, const int32_t* cta_group,
                                          const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
                                          const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
                                          const int64_t* cta_part_ptr, void* part, const void* x, void* y,
@@ -414,6 +472,7 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   if (n_cols < 0 || n_ctas < 0 || n_long < 0 || max_group_acc < 0 || max_group_acc >= 65535) return FSB_EINVAL;
   if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
   if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
+  if (fsb_spmv_panel_piece_slots(rounds) == 0) return FSB_EINVAL;
   if (n_long == 0 || n_ctas == 0) return FSB_OK;
   if (!val || !rc || !unit_piece_ptr || !unit_chunk || !cta_unit_ptr || !cta_group || !group_q_ptr ||
       !group_cta_ptr || !vbase || !q_group || !long_rows || !cta_part_ptr || !part || !x || !y)
@@ -421,21 +480,32 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
+  const bool check = (flags & FSB_PANEL_LONG_RUNS) != 0;
+  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0};
   const unsigned rgrid = (unsigned)((n_long + 255) / 256);
-#define FSB_GROUPS_LAUNCH(V)                                                                                       \
-  do {                                                                                                             \
-    cudaError_t e = cudaFuncSetAttribute(spmv_panel_groups_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                               \
-    if (e != cudaSuccess) return cuda_rc(e);                                                                       \
-    spmv_panel_groups_kernel<V><<<(unsigned)n_ctas, kPanelThreads, smem, st>>>(                                    \
-        (const V*)val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr, cta_group, group_q_ptr, vbase, cta_part_ptr,  \
-        (V*)part, (const V*)x, n_cols, chunk_cols, n_buffers, status);                                             \
-    FSB_RETURN_IF_LAUNCH_FAILED();                                                                                 \
-    panel_group_reduce_kernel<V><<<rgrid, 256, 0, st>>>((const V*)part, q_group, group_q_ptr, group_cta_ptr,       \
-                                                        cta_part_ptr, long_rows, (V*)y, n_long);                   \
+#define FSB_GROUPS_LAUNCH_(K)                                                                                    \
+  do {                                                                                                           \
+    cudaError_t e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+    if (e != cudaSuccess) return cuda_rc(e);                                                                     \
+    K<<<(unsigned)n_ctas, kPanelThreads, smem, st>>>((const VT_*)val, rc, unit_piece_ptr, unit_chunk,            \
+                                                     cta_unit_ptr, cta_group, group_q_ptr, vbase, cta_part_ptr,  \
+                                                     (VT_*)part, (const VT_*)x, gm, status);                     \
   } while (0)
-  if (vtype == FSB_F32) FSB_GROUPS_LAUNCH(float); else FSB_GROUPS_LAUNCH(double);
-#undef FSB_GROUPS_LAUNCH
+  if (vtype == FSB_F32) {
+    typedef float VT_;
+    FSB_PANEL_DISPATCH(spmv_panel_groups_kernel, float, FSB_GROUPS_LAUNCH_);
+    FSB_RETURN_IF_LAUNCH_FAILED();
+    panel_group_reduce_kernel<float><<<rgrid, 256, 0, st>>>((const float*)part, q_group, group_q_ptr, group_cta_ptr,
+                                                             cta_part_ptr, long_rows, (float*)y, n_long);
+  } else {
+    typedef double VT_;
+    FSB_PANEL_DISPATCH(spmv_panel_groups_kernel, double, FSB_GROUPS_LAUNCH_);
+    FSB_RETURN_IF_LAUNCH_FAILED();
+    panel_group_reduce_kernel<double><<<rgrid, 256, 0, st>>>((const double*)part, q_group, group_q_ptr,
+                                                              group_cta_ptr, cta_part_ptr, long_rows, (double*)y,
+                                                              n_long);
+  }
+#undef FSB_GROUPS_LAUNCH_
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }

@@ -9,8 +9,8 @@ entry through L2.  What remains (short rows only) goes through the CSR kernels.
 
 Layout of the long part (csrc/spmv_panel.cu, spmv_panel_groups_kernel):
   * the long rows, longest first, are numbered q = 0 .. n_long-1;
-  * a row with more than 16 entries in some chunk gets several accumulators ("virtual rows"), 16 entries of a
-    chunk to each, so that the kernel's rule of at most 16 entries per accumulator and unit holds;
+  * a row with more entries in some chunk than a lane of the kernel has rounds (16) gets several accumulators
+    ("virtual rows"), that many entries of a chunk to each, so that no two lanes finish on one accumulator;
   * consecutive rows form groups whose accumulators fit in shared memory; units = (group, chunk), ordered by
     group then chunk, are dealt to about one CTA per SM in proportion to their cost (entries streamed plus the
     chunk of x), never mixing groups in a CTA;
@@ -40,8 +40,8 @@ ACC_CAP = None              # accumulators per group; None = what fits in shared
 class LongRowLayout:
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "cta_unit_ptr", "cta_group", "group_q_ptr",
                  "group_cta_ptr", "vbase", "q_group", "long_rows", "cta_part_ptr", "part", "n_ctas", "n_groups",
-                 "n_long", "chunk_cols", "n_buffers", "max_group_acc", "n_units", "n_pieces", "nnz", "x_overhead",
-                 "slot_overhead", "status")
+                 "n_long", "chunk_cols", "n_buffers", "rounds", "flags", "max_group_acc", "n_units", "n_pieces", "nnz",
+                 "x_overhead", "slot_overhead", "status")
 
     def nbytes(self):
         names = ("val", "rc", "unit_piece_ptr", "unit_chunk", "cta_unit_ptr", "cta_group", "group_q_ptr",
@@ -86,7 +86,10 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     dev = data.device
     sv = data.element_size()
     CW = chunk_cols or int(os.environ.get("FSB_PANEL_CHUNK", "0")) or (8192 if sv == 4 else 4096)
-    SLOTS = int(_lib.lib().fsb_spmv_panel_piece_slots())
+    # a (row, chunk) run is cut into virtual rows of at most `rounds` entries, so no piece needs the kernel's
+    # segmented path
+    rounds = _panel.default_rounds() or _panel.ROUNDS[-1]
+    SLOTS = int(_lib.lib().fsb_spmv_panel_piece_slots(rounds))
     NB = _panel.default_buffers()
     cap = acc_cap or ACC_CAP or _accumulator_cap(data.dtype, CW, NB)
     if n_ctas_target is None:
@@ -119,7 +122,7 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     ar = torch.arange(nnz, device=dev)
     run_first = ar[first]
     j = ar - run_first[torch.cumsum(first.to(torch.int64), 0) - 1]      # position inside the (row, chunk) run
-    sub_sorted = j >> 4
+    sub_sorted = j // rounds
     del first, run_first, j, k1
     q_sorted = q_of[perm1]
     nv = torch.zeros(n_long, dtype=torch.int64, device=dev)
@@ -189,12 +192,12 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     vrow_p = vbase[q_p] + sub_p                                          # global accumulator number = run key
     acc_p = vrow_p - group_vb[q_group[q_p]]
     del q_p, sub_p
-    packed = _panel.pack_pieces(data[src[perm]], acc_p, cols[perm], vrow_p, unit_of_entry, ustart, u_ord, CW, SLOTS,
+    packed = _panel.pack_pieces(data[src[perm]], acc_p, cols[perm], vrow_p, unit_of_entry, ustart, u_ord, CW, rounds,
                                 None, n_buffers=NB)
     del acc_p, vrow_p, unit_of_entry, src, cols, perm
     if packed is None:
         return None
-    val, rc, upiece, n_pieces = packed
+    val, rc, upiece, n_pieces, max_run = packed
 
     lay = LongRowLayout()
     lay.val, lay.rc = val, rc
@@ -207,23 +210,27 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     lay.part = torch.zeros(max(1, int(cta_part_ptr[-1].item())), dtype=data.dtype, device=dev)
     lay.n_ctas, lay.n_groups, lay.n_long = n_ctas, n_groups, n_long
     lay.chunk_cols, lay.n_buffers, lay.max_group_acc = CW, NB, max_group_acc
+    lay.rounds, lay.flags = rounds, (_panel.FLAG_LONG_RUNS if max_run > rounds else 0)
     lay.n_units, lay.n_pieces, lay.nnz = n_units, n_pieces, nnz
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)
-    lay.status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lay.status = _panel.StatusWord(dev)
     mask = torch.zeros_like(is_long)
     mask[long_rows] = True
     return lay, mask
 
 
-def launch_long_rows(layout, x, y, n_cols, stream_ptr):
+def launch_long_rows(layout, x, y, n_cols, stream_ptr, flags=0):
     """y[long rows] = (A x)[long rows]; the other elements of y are left alone."""
     la = layout
+    la.status.poll()
     rc = _lib.lib().fsb_spmv_csr_panel_groups(
         _VTYPE[la.val.dtype], la.val.data_ptr(), la.rc.data_ptr(), la.unit_piece_ptr.data_ptr(),
-        la.unit_chunk.data_ptr(), la.cta_unit_ptr.data_ptr(), la.n_ctas, la.chunk_cols, la.n_buffers, la.max_group_acc,
+        la.unit_chunk.data_ptr(), la.cta_unit_ptr.data_ptr(), la.n_ctas, la.chunk_cols, la.n_buffers, la.rounds,
+        la.flags | flags, la.max_group_acc,
         la.cta_group.data_ptr(), la.group_q_ptr.data_ptr(), la.group_cta_ptr.data_ptr(), la.vbase.data_ptr(),
         la.q_group.data_ptr(), la.long_rows.data_ptr(), la.n_long, la.cta_part_ptr.data_ptr(), la.part.data_ptr(),
         x.data_ptr(), y.data_ptr(), n_cols, la.status.data_ptr(), stream_ptr,
     )
     _lib.check(rc, "fsb_spmv_csr_panel_groups")
+    la.status.posted("fsb_spmv_csr_panel_groups")

@@ -12,7 +12,7 @@ import os
 import torch
 
 from . import _lib
-from ._common import _VTYPE
+from ._common import StatusWord, _VTYPE
 
 SM_COUNT_FALLBACK = 148
 CTAS_PER_SM = 1              # one 1024-thread CTA (row block) per SM
@@ -24,7 +24,12 @@ MAX_X_OVERHEAD = 1.3
 MAX_X_OVERHEAD_F64 = 0.8
 MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
 N_BUFFERS = 2               # chunks of x in shared memory (fetched N_BUFFERS - 1 units ahead)
-MAX_RUN = 16                # entries of one row inside one unit = rounds per piece (see csrc/spmv_panel.cu)
+ROUNDS = (4, 8, 16)         # slots per lane and piece the kernel is built for (see csrc/spmv_panel.cu)
+# a piece whose lanes finish on a common row (a row with more than `rounds` entries in the unit) takes the kernel's
+# slower segmented path: small pieces are chosen only while that stays rare
+MAX_SLOW_PIECES = 0.02
+FLAG_LONG_RUNS = 1          # FSB_PANEL_LONG_RUNS
+FLAG_DEBUG_TIMEOUT = 256    # FSB_PANEL_DEBUG_TIMEOUT
 MAX_ROW_NNZ = 512
 MIN_NNZ = 1 << 22
 NO_ROW = 0xFFFF
@@ -34,7 +39,8 @@ class PanelLayout:
     """Device arrays of the regrouped matrix plus the launch geometry."""
 
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "rb_unit_ptr", "n_row_blocks", "rb_rows", "chunk_cols",
-                 "n_buffers", "n_units", "n_pieces", "x_overhead", "slot_overhead", "status")
+                 "n_buffers", "rounds", "flags", "max_run", "n_units", "n_pieces", "x_overhead", "slot_overhead",
+                 "status")
 
     def nbytes(self):
         return sum(t.numel() * t.element_size() for t in (self.val, self.rc, self.unit_piece_ptr, self.unit_chunk,
@@ -48,6 +54,12 @@ def smem_budget():
 
 def default_buffers():
     return int(os.environ.get("FSB_PANEL_BUFFERS", "0")) or N_BUFFERS
+
+
+def default_rounds():
+    """FSB_PANEL_ROUNDS=4|8|16 fixes the piece size; unset, build_panel_layout picks it from the run lengths."""
+    r = int(os.environ.get("FSB_PANEL_ROUNDS", "0"))
+    return r if r in ROUNDS else None
 
 
 def _geometry(dtype, n_rows, device, n_buffers):
@@ -70,7 +82,7 @@ def _geometry(dtype, n_rows, device, n_buffers):
     n_blocks = -(-n_blocks // slots_gpu) * slots_gpu
     rb_rows = min(rb_cap, max(1024, -(-n_rows // n_blocks)))
     rb_rows = -(-rb_rows // 4) * 4
-    return vt, sv, chunk_cols, rb_rows, int(L.fsb_spmv_panel_piece_slots())
+    return vt, sv, chunk_cols, rb_rows
 
 
 SLAB_NNZ = 1 << 27           # the regrouping works on this many entries at a time (bounds its temporaries)
@@ -92,26 +104,57 @@ def _slabs(indptr, n_rows, rb_rows, slab_nnz=None):
     return out
 
 
-def estimate_units(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
-    """Number of non-empty (row block, column chunk) units, without sorting anything."""
+def scan_structure(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
+    """(number of non-empty (row block, column chunk) units, [runs longer than 4, 8, 16 entries]) without sorting
+    anything; a run = consecutive entries of one row inside one column chunk (rows with sorted columns: all of the
+    row's entries in that chunk).  None when the unit grid is too large to mark."""
     n_rb = -(-n_rows // rb_rows)
     n_ch = -(-n_cols // chunk_cols)
     if n_rb * n_ch > (1 << 31):
         return None
     total = 0
+    long_runs = [0, 0, 0]
+    dev = indices.device
     for r0, r1 in _slabs(indptr, n_rows, rb_rows):
         e0, e1 = int(indptr[r0]), int(indptr[r1])
         if e1 == e0:
             continue
         lens = (indptr[r0 + 1:r1 + 1] - indptr[r0:r1]).to(torch.int64)
-        rows = torch.repeat_interleave(torch.arange(r0, r1, device=indices.device), lens)
+        rows = torch.repeat_interleave(torch.arange(r0, r1, device=dev), lens)
         b0 = r0 // rb_rows
-        key = (rows // rb_rows - b0) * n_ch + indices[e0:e1].to(torch.int64) // chunk_cols
-        mark = torch.zeros((-(-(r1 - r0) // rb_rows)) * n_ch, dtype=torch.bool, device=indices.device)
+        chunk = indices[e0:e1].to(torch.int64) // chunk_cols
+        key = (rows // rb_rows - b0) * n_ch + chunk
+        mark = torch.zeros((-(-(r1 - r0) // rb_rows)) * n_ch, dtype=torch.bool, device=dev)
         mark[key] = True
         total += int(mark.sum().item())
-        del lens, rows, key, mark
-    return total
+        del key, mark
+        run_key = rows * n_ch + chunk
+        del rows, chunk, lens
+        start = torch.ones(e1 - e0, dtype=torch.bool, device=dev)
+        start[1:] = run_key[1:] != run_key[:-1]
+        del run_key
+        first = torch.nonzero(start, as_tuple=False).flatten()
+        del start
+        length = torch.diff(first, append=torch.tensor([e1 - e0], device=dev))
+        for k, bound in enumerate(ROUNDS):
+            long_runs[k] += int((length > bound).sum().item())
+        del first, length
+    return total, long_runs
+
+
+def estimate_units(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
+    """Number of non-empty (row block, column chunk) units, without sorting anything."""
+    scan = scan_structure(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols)
+    return None if scan is None else scan[0]
+
+
+def choose_rounds(nnz, long_runs):
+    """Smallest piece (rounds per lane) for which the pieces that need the kernel's segmented path stay rare."""
+    for k, rounds in enumerate(ROUNDS):
+        n_pieces = max(1.0, nnz / (32.0 * rounds))
+        if long_runs[k] <= MAX_SLOW_PIECES * n_pieces:
+            return rounds
+    return ROUNDS[-1]
 
 
 def _cumsum0(counts):
@@ -120,16 +163,17 @@ def _cumsum0(counts):
     return out
 
 
-def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, SLOTS, max_slot_overhead,
+def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, rounds, max_slot_overhead,
                 n_buffers=2):
-    """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of SLOTS slots and
-    lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that follow each
-    other with the same key inside one unit form a run, which must not straddle two pieces and may have at most
-    MAX_RUN entries.  Returns (val, rc, first piece of each unit [n_units + 1], n_pieces), or None when a run is
-    too long or the padding exceeds max_slot_overhead."""
+    """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of 32 * rounds
+    slots and lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that
+    follow each other with the same key inside one unit form a run, which must not straddle two pieces.  Returns
+    (val, rc, first piece of each unit [n_units + 1], n_pieces, longest run), or None when a run does not fit in
+    a piece or the padding exceeds max_slot_overhead."""
     dev = data_p.device
     nnz = data_p.numel()
     sv = data_p.element_size()
+    SLOTS = 32 * rounds
     ar = torch.arange(nnz, device=dev)
     new_run = torch.ones(nnz, dtype=torch.bool, device=dev)
     new_run[1:] = (run_key_p[1:] != run_key_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
@@ -141,7 +185,7 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     run_end[-1] = nnz
     max_run = int((run_end - run_first).max().item())
     del run_end, new_run
-    if max_run > MAX_RUN:
+    if max_run > SLOTS:
         return None
     # Pieces: greedy packing of whole runs into pieces of at most SLOTS entries, all units advancing one
     # piece per step (the cut after a piece that starts at s is the last run boundary at or before s + SLOTS).
@@ -168,16 +212,16 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
         return None
     piece = torch.searchsorted(piece_start, ar, right=True) - 1
     slot = ar - piece_start[piece]
-    # inside a piece, slot = 16 * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
+    # inside a piece, slot = rounds * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
     # contiguous: values at (k // E) * 32 * E + lane * E + k % E (E = values per 16 bytes), words with E = 4
-    lane_, k_ = slot >> 4, slot & 15
+    lane_, k_ = slot // rounds, slot % rounds
     E = 16 // sv
     pos_val = piece * SLOTS + (k_ // E) * (32 * E) + lane_ * E + k_ % E
     pos = piece * SLOTS + (k_ >> 2) * 128 + lane_ * 4 + (k_ & 3)
     del lane_, k_, slot, piece, ar
     upiece = torch.searchsorted(piece_start, ustart)            # first piece of each unit (and the total)
     del piece_start
-    field = (u_ord[unit_of_entry] & (n_buffers - 1)) * CW + (cols_p - (cols_p // CW) * CW)
+    field = (u_ord[unit_of_entry] % n_buffers) * CW + (cols_p - (cols_p // CW) * CW)
     val = torch.zeros(n_pieces * SLOTS, dtype=data_p.dtype, device=dev)
     val[pos_val] = data_p
     del pos_val
@@ -186,13 +230,13 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)
     rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
     rc[pos] = word
-    return val, rc, upiece, n_pieces
+    return val, rc, upiece, n_pieces, max_run
 
 
-def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, SLOTS, NB, max_slot_overhead):
+def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slot_overhead):
     """The units and pieces of rows r0 .. r1-1 (whole row blocks).  Returns (val, rc, first piece of each unit + total,
-    chunk of each unit, row block of each unit, number of pieces); () when the rows hold no entry; None when the
-    rows cannot be laid out."""
+    chunk of each unit, row block of each unit, number of pieces, longest run); () when the rows hold no entry;
+    None when the rows cannot be laid out."""
     dev = data.device
     e0, e1 = int(indptr[r0]), int(indptr[r1])
     if e1 == e0:
@@ -219,14 +263,14 @@ def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, SLOTS, NB, max_slot
     first_unit = torch.searchsorted(u_rb.contiguous(), torch.arange(b0, b0 + n_b, device=dev))
     u_ord = torch.arange(n_units, device=dev) - first_unit[u_rb - b0]
     packed = pack_pieces(data[e0:e1][perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord,
-                         CW, SLOTS, max_slot_overhead, n_buffers=NB)
+                         CW, rounds, max_slot_overhead, n_buffers=NB)
     if packed is None:
         return None
-    val, rc, upiece, n_pieces = packed
-    return val, rc, upiece, u_ch, u_rb, n_pieces
+    val, rc, upiece, n_pieces, max_run = packed
+    return val, rc, upiece, u_ch, u_rb, n_pieces, max_run
 
 
-def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False):
+def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False, rounds=None):
     """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
     nnz = data.numel()
     if nnz == 0 or n_rows == 0 or n_cols == 0:
@@ -238,30 +282,45 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     geometry = _geometry(data.dtype, n_rows, dev, NB)
     if geometry is None:
         return None
-    vt, sv, CW, RB, SLOTS = geometry
+    vt, sv, CW, RB = geometry
     n_rb = -(-n_rows // RB)
     n_ch = -(-n_cols // CW)
-    if not force:
-        n_units = estimate_units(indices, indptr, n_rows, n_cols, RB, CW)
-        limit = MAX_X_OVERHEAD if sv == 4 else MAX_X_OVERHEAD_F64
-        if n_units is None or n_units * CW * sv > limit * nnz * (sv + 4):
-            return None
+    rounds = rounds or default_rounds()
+    if not force or rounds is None:
+        scan = scan_structure(indices, indptr, n_rows, n_cols, RB, CW)
+        if scan is None:
+            if not force:
+                return None
+            rounds = rounds or ROUNDS[-1]
+        else:
+            n_units, long_runs = scan
+            limit = MAX_X_OVERHEAD if sv == 4 else MAX_X_OVERHEAD_F64
+            if not force and n_units * CW * sv > limit * nnz * (sv + 4):
+                return None
+            rounds = rounds or choose_rounds(nnz, long_runs)
+    SLOTS = 32 * rounds
     vals, rcs, upieces, chunks, blocks = [], [], [], [], []
     piece_base = 0
+    max_run = 0
     for r0, r1 in _slabs(indptr, n_rows, RB):
-        part = _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, SLOTS, NB,
+        part = _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB,
                            None if force else MAX_SLOT_OVERHEAD)
         if part is None:
+            if rounds < ROUNDS[-1]:
+                # a run that does not fit in a small piece (or too much padding): the largest piece may still do
+                del vals, rcs
+                return build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force, ROUNDS[-1])
             return None
         if part == ():
             continue                 # no entries in these rows
-        val_s, rc_s, upiece_s, u_ch_s, u_rb_s, n_pieces_s = part
+        val_s, rc_s, upiece_s, u_ch_s, u_rb_s, n_pieces_s, max_run_s = part
         vals.append(val_s)
         rcs.append(rc_s)
         upieces.append(upiece_s[:-1] + piece_base)
         chunks.append(u_ch_s)
         blocks.append(u_rb_s)
         piece_base += n_pieces_s
+        max_run = max(max_run, max_run_s)
     n_pieces = piece_base
     if n_pieces >= 2**31 - 1:
         return None
@@ -281,19 +340,26 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     lay.unit_chunk = u_ch.to(torch.int32)
     lay.rb_unit_ptr = rb_unit_ptr.to(torch.int32)
     lay.n_row_blocks, lay.rb_rows, lay.chunk_cols, lay.n_buffers = n_rb, RB, CW, NB
+    lay.rounds, lay.max_run = rounds, max_run
+    lay.flags = FLAG_LONG_RUNS if max_run > rounds else 0
     lay.n_units, lay.n_pieces = n_units, n_pieces
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)
-    lay.status = torch.zeros(1, dtype=torch.int32, device=dev)
+    lay.status = StatusWord(dev)
     return lay
 
 
-def launch_panel(layout, x, y, n_rows, n_cols, stream_ptr):
+def launch_panel(layout, x, y, n_rows, n_cols, stream_ptr, block_begin=0, block_end=None, flags=0, record_on=None):
+    """Enqueue the product (or the row blocks [block_begin, block_end) of it) on the stream behind stream_ptr;
+    record_on: the torch stream object of that stream when it is not the current one."""
     L = _lib.lib()
+    layout.status.poll()
     rc = L.fsb_spmv_csr_panel(
         _VTYPE[layout.val.dtype], layout.val.data_ptr(), layout.rc.data_ptr(), layout.unit_piece_ptr.data_ptr(),
         layout.unit_chunk.data_ptr(), layout.rb_unit_ptr.data_ptr(), layout.n_row_blocks, layout.rb_rows,
-        layout.chunk_cols, layout.n_buffers, x.data_ptr(), y.data_ptr(), n_rows, n_cols, layout.status.data_ptr(),
-        stream_ptr,
+        layout.chunk_cols, layout.n_buffers, layout.rounds, layout.flags | flags, block_begin,
+        layout.n_row_blocks if block_end is None else block_end, x.data_ptr(), y.data_ptr(), n_rows, n_cols,
+        layout.status.data_ptr(), stream_ptr,
     )
     _lib.check(rc, "fsb_spmv_csr_panel")
+    layout.status.posted("fsb_spmv_csr_panel", record_on)

@@ -22,6 +22,7 @@ from ._common import (
     _analyze_csr,
     _check_value_dtype,
     _ptr,
+    StatusWord,
     _stream_ptr,
     _tile_plan,
 )
@@ -202,8 +203,18 @@ class PreparedCsrSpmmOpt:
 
     def status_word(self):
         if self._status is None:
-            self._status = torch.zeros(1, dtype=torch.int32, device=self.data.device)
+            self._status = StatusWord(self.data.device)
         return self._status
+
+    def check_status(self):
+        """Wait for the last product on this matrix and raise RuntimeError if its kernel gave up on a bounded
+        device-side wait (tiles of C are then unwritten).  Every product also looks, without waiting, at how the
+        previous one ended."""
+        if self._status is not None:
+            self._status.check()
+        if self.wide is not None:
+            for part in self.wide[1]:
+                part.check_status()
 
 
 def prepare_spmm_csr_opt(data, indices, indptr, shape):
@@ -236,6 +247,7 @@ def _spmm_launch(prepared, B, C):
         return
     algo = _SPMM_ALGO_NAMES.get(os.environ.get("FSB_SPMM_ALGO", "auto").strip().lower(), _lib.FSB_SPMM_AUTO)
     scratch = p.scratch_for(n_dense) if p.tile_row is not None else None
+    p.status_word().poll()
     with torch.cuda.device(dev):
         rc = L.fsb_spmm_csr(
             _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
@@ -246,6 +258,7 @@ def _spmm_launch(prepared, B, C):
             p.status_word().data_ptr(), _stream_ptr(dev),
         )
     _lib.check(rc, "fsb_spmm_csr")
+    p.status_word().posted("fsb_spmm_csr")
 
 
 def _check_out(out, device, shape, dtype, device_msg):
@@ -286,6 +299,7 @@ def _run_spmm(prepared, B, out, return_time):
     if return_time:
         torch.cuda.synchronize(dev)
         elapsed_ms = (time.perf_counter() - t0) * 1000.0
+        prepared.check_status()
     if out is not None and not direct:
         out.copy_(C)
         C = out

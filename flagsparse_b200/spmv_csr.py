@@ -120,6 +120,23 @@ class PreparedCsrSpmv:
             kind = "long-row panel + " + long_rows[0].opt_buckets[0]["kind"]
         self.opt_buckets = [{"kind": kind, "tile_nnz": tile_nnz, "n_tiles": n_tiles, "n_rows": n_rows}]
 
+    def _status_words(self):
+        if self.panel is not None:
+            yield self.panel.status
+        if self.long_rows is not None:
+            yield self.long_rows[1].status
+            yield from self.long_rows[0]._status_words()
+        if self.wide is not None:
+            for part in self.wide[1]:
+                yield from part._status_words()
+
+    def check_status(self):
+        """Wait for the last product on this matrix and raise RuntimeError if one of its kernels gave up on a
+        bounded device-side wait (its rows of y are then incomplete).  Every product also looks, without waiting,
+        at how the previous one ended."""
+        for word in self._status_words():
+            word.check()
+
 
 def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
     """Validate and normalise the CSR arrays; same checks, order and exception types as the reference's
@@ -328,6 +345,7 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
         if return_time:
             torch.cuda.synchronize(dev)
             elapsed_ms = (time.perf_counter() - t0) * 1000.0
+            prepared.check_status()
         if out is not None:
             out.copy_(y)
             y = out
@@ -344,6 +362,7 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
     if return_time:
         torch.cuda.synchronize(dev)
         elapsed_ms = (time.perf_counter() - t0) * 1000.0
+        prepared.check_status()
     if out is not None and not direct:
         out.copy_(y)
         y = out

@@ -112,51 +112,54 @@ int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, const void* 
  * box, the local one included) through peer-mapped pointers, at element offset row_offset + i: the
  * SpMV epilogue doubles as the all-gather of the row-sharded driver.  y_peers is a DEVICE array of
  * n_peers pointers.  algo: FSB_SPMV_VECTOR (no plan, no scratch) or FSB_SPMV_STREAM, as for fsb_spmv_csr;
- * FSB_SPMV_AUTO takes STREAM when tile_row and scratch are given.  The reference has no multi-GPU path; this
+ * FSB_SPMV_AUTO takes STREAM when tile_row and scratch are given.  first_peer = this GPU's index in y_peers: the
+ * destinations are visited in an order rotated by it (and by the CTA), so that the GPUs of a box do not all write
+ * to the same destination at once.  The reference has no multi-GPU path; this
  * stands in for "each rank runs spmv_csr.py:329-376 on its row shard, then y is all-gathered".
  */
 int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, const void* indices,
-                         const void* indptr, const void* x, void* const* y_peers, int n_peers,
+                         const void* indptr, const void* x, void* const* y_peers, int n_peers, int first_peer,
                          int64_t row_offset, int64_t n_rows, int64_t n_cols, int64_t nnz, int algo, int tuning,
                          const int32_t* tile_row, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
  * y = A x from the "panel" regrouping of a CSR matrix (built once per matrix by the host code,
  * flagsparse_b200/panel.py): entries grouped into units = (block of rb_rows rows) x (chunk of chunk_cols
- * columns), row-major inside a unit, each unit cut into pieces of fsb_spmv_panel_piece_slots() slots so
- * that no row's entries straddle two pieces.
+ * columns), row-major inside a unit, each unit cut into pieces of fsb_spmv_panel_piece_slots(rounds) =
+ * 32 * rounds slots so that no row's entries straddle two pieces.
  *   val[s], rc[s]        per slot: value and packed word (local row << 16 | buffer * chunk_cols + local
  *                        column), buffer = ordinal of the unit inside its row block modulo n_buffers; unused
  *                        slots carry local row 0xFFFF
- *   n_buffers            2, 4 or 8 chunks of x in shared memory (n_buffers * chunk_cols <= 65536): chunks are
+ *   rounds               4, 8 or 16: slots per lane and piece.  Small pieces suit units with few entries
+ *                        (every warp of the CTA gets work in every unit)
+ *   flags                FSB_PANEL_LONG_RUNS: some row has more than `rounds` entries inside one unit (never
+ *                        more than a piece holds); the kernel then combines the lanes that finish on the same
+ *                        row.  FSB_PANEL_DEBUG_TIMEOUT (tests only): the first copy of x of every CTA is made to
+ *                        look incomplete and the wait limit is lowered, so that the kernel takes its time-out
+ *                        path -- it reports through `status` and returns without touching y
+ *   n_buffers            2..8 chunks of x in shared memory (n_buffers * chunk_cols <= 65536): chunks are
  *                        fetched n_buffers - 1 units ahead of their use
  *   unit_piece_ptr       pieces [unit_piece_ptr[u], unit_piece_ptr[u+1]) belong to unit u
  *   unit_chunk           column chunk of unit u
  *   rb_unit_ptr          units [rb_unit_ptr[b], rb_unit_ptr[b+1]) belong to row block b, in chunk order
+ *   block_begin/_end     the launch covers row blocks [block_begin, block_end) only (rows block_begin * rb_rows
+ *                        onward); the row-sharded driver issues one launch per slice of its shard and ships a
+ *                        finished slice to the other GPUs while the next one is computed
  * One CTA per row block keeps the block's y accumulators and n_buffers chunks of x in shared memory
  * (fsb_spmv_panel_smem_bytes() + fsb_spmv_panel_static_smem_bytes() must fit in 227 KiB; rb_rows < 65535).  Another stand-in for the launches of
  * _triton_spmv_csr_impl_opt_prepared (spmv_csr.py:329-376), for matrices whose rows span few column chunks.
  * status: optional device int32, set non-zero if a bounded wait on a bulk copy of x ran out.
  */
-int fsb_spmv_panel_piece_slots(void);
+#define FSB_PANEL_LONG_RUNS 1
+#define FSB_PANEL_DEBUG_TIMEOUT 256
+int fsb_spmv_panel_piece_slots(int rounds);
 size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers);
 size_t fsb_spmv_panel_static_smem_bytes(void);
 int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                        const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
-                       int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x, void* y,
-                       int64_t n_rows, int64_t n_cols, int32_t* status, void* stream);
-
-/*
- * The same product for one shard of a row-sharded matrix: row i of the shard is stored to
- * y_peers[p][row_offset + i] for every p in [0, n_peers) -- y_peers is a DEVICE array of n_peers device pointers
- * (this GPU's buffer and the peer-mapped buffers of the other GPUs), as for fsb_spmv_csr_scatter.  No counterpart
- * in the reference (single GPU).
- */
-int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
-                               const int32_t* unit_chunk, const int32_t* rb_unit_ptr, int32_t n_row_blocks,
-                               int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, const void* x,
-                               void* const* y_peers, int n_peers, int64_t row_offset, int64_t n_rows,
-                               int64_t n_cols, int32_t* status, void* stream);
+                       int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, int32_t rounds, int32_t flags,
+                       int32_t block_begin, int32_t block_end, const void* x, void* y, int64_t n_rows,
+                       int64_t n_cols, int32_t* status, void* stream);
 
 /*
  * Row-group form of the panel product, for the LONG rows of a skewed matrix: y[long_rows[q]] = (A x)[long_rows[q]]
@@ -164,7 +167,7 @@ int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc, c
  * short rows first).  Replaces, for those rows, the long-row buckets of _triton_spmv_csr_impl_opt_prepared
  * (spmv_csr.py:329-376 with the bucket tables :64-89: one Triton program per long row).
  * The picked rows are cut into groups; row q owns accumulators vbase[q] .. vbase[q+1]-1 ("virtual rows": at most
- * 16 entries of a virtual row in one column chunk) and the packed word of a slot holds the virtual row relative
+ * `rounds` entries of a virtual row in one column chunk) and the packed word of a slot holds the virtual row relative
  * to its group.  The units (group x column chunk) are ordered by group, then chunk, and dealt to n_ctas CTAs:
  *   cta_unit_ptr         units [cta_unit_ptr[c], cta_unit_ptr[c+1]) belong to CTA c (buffer of a slot's packed
  *                        word = ordinal of the unit inside its CTA modulo n_buffers)
@@ -174,11 +177,12 @@ int fsb_spmv_csr_panel_scatter(int vtype, const void* val, const uint32_t* rc, c
  *   cta_part_ptr, part   CTA c writes one partial sum per row of its group to part[cta_part_ptr[c] + ...]; a
  *                        second kernel adds the partial sums of a row in CTA order (in double) and stores y.
  *                        part must hold sum over CTAs of the row count of their group, in elements of vtype.
- * Everything else as for fsb_spmv_csr_panel.  Results are bit-reproducible.
+ * Everything else (rounds and flags included) as for fsb_spmv_csr_panel.  Results are bit-reproducible.
  */
 int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
                               const int32_t* unit_chunk, const int32_t* cta_unit_ptr, int32_t n_ctas,
-                              int32_t chunk_cols, int32_t n_buffers, int32_t max_group_acc, const int32_t* cta_group,
+                              int32_t chunk_cols, int32_t n_buffers, int32_t rounds, int32_t flags,
+                              int32_t max_group_acc, const int32_t* cta_group,
                               const int32_t* group_q_ptr, const int32_t* group_cta_ptr, const int32_t* vbase,
                               const int32_t* q_group, const int32_t* long_rows, int32_t n_long,
                               const int64_t* cta_part_ptr, void* part, const void* x, void* y, int64_t n_cols,

@@ -14,6 +14,8 @@ from oracle import csr_oracle as O
 
 def _evaluate(lay, x, n_rows, n_cols, slots):
     """y from the layout the way the kernel walks it (row block -> units -> pieces -> slots)."""
+    R = lay.rounds
+    assert slots == 32 * R
     y = np.zeros(n_rows)
     val = lay.val.numpy().astype(np.float64)
     rc = lay.rc.numpy().astype(np.int64) & 0xFFFFFFFF
@@ -24,21 +26,26 @@ def _evaluate(lay, x, n_rows, n_cols, slots):
     for b in range(lay.n_row_blocks):
         assert np.all(np.diff(uch[rbp[b]:rbp[b + 1]]) > 0)   # units of a row block in chunk order
         for u in range(rbp[b], rbp[b + 1]):
-            parity = (u - rbp[b]) & (lay.n_buffers - 1)
+            parity = (u - rbp[b]) % lay.n_buffers
             rows_in_unit = []
             for pc in range(upp[u], upp[u + 1]):
-                # undo the interleaving: slot = 16 * lane + k
+                # undo the interleaving: slot = R * lane + k
                 sl = np.arange(slots)
-                ln, k = sl // 16, sl % 16
+                ln, k = sl // R, sl % R
                 E = 16 // lay.val.element_size()
                 w = rc[pc * slots + (k // 4) * 128 + ln * 4 + k % 4]
                 vals = val[pc * slots + (k // E) * 32 * E + ln * E + k % E]
                 rloc, field = w >> 16, w & 0xFFFF
-                # the kernel's race-freedom: the 32 slots of a round (same position modulo 16) hold 32 different rows
-                for k in range(16):
-                    rk = rloc[k::16]
-                    rk = rk[rk != 0xFFFF]
-                    assert rk.size == np.unique(rk).size
+                # the kernel's race-freedom: a lane adds to an accumulator where its row ends.  In every round but a
+                # lane's last one the lanes that do so are on different rows; in the last round two lanes may meet
+                # only in layouts flagged for the kernel's segmented path
+                nxt = np.append(rloc[1:], 0xFFFF)
+                nxt[R - 1::R] = 0xFFFF                      # a lane's run ends with its last slot
+                ends = (rloc != 0xFFFF) & (nxt != rloc)
+                for k in range(R):
+                    rk = rloc[k::R][ends[k::R]]
+                    if k < R - 1 or not (lay.flags & panel.FLAG_LONG_RUNS):
+                        assert rk.size == np.unique(rk).size
                 live = rloc != 0xFFFF
                 assert live.any() and np.all(live[:live.sum()])            # real slots first, then padding
                 assert np.all(vals[~live] == 0)
@@ -55,14 +62,20 @@ def _evaluate(lay, x, n_rows, n_cols, slots):
     return y, seen
 
 
+@pytest.mark.parametrize("rounds", [None, 4, 8, 16])
 @pytest.mark.parametrize("vdt", ["float32", "float64"])
-def test_layout_of_a_banded_matrix(fsb_lib, vdt):
+def test_layout_of_a_banded_matrix(fsb_lib, vdt, rounds):
     spec = S.config_spec("c2").scaled(120000)
     d, i, p = (torch.from_numpy(a) for a in S.generate_csr(spec, None, value_dtype=vdt))
-    lay = panel.build_panel_layout(d, i, p, spec.n_rows, spec.n_cols, 70, force=True)
+    lay = panel.build_panel_layout(d, i, p, spec.n_rows, spec.n_cols, 70, force=True, rounds=rounds)
     assert lay is not None and lay.n_row_blocks * lay.rb_rows >= spec.n_rows
+    assert lay.rounds == (rounds or lay.rounds) and lay.rounds in panel.ROUNDS
+    # rows of this matrix have up to a dozen entries in a chunk: small pieces must carry the long-run flag
+    assert bool(lay.flags & panel.FLAG_LONG_RUNS) == (lay.max_run > lay.rounds)
+    if rounds == 4:
+        assert lay.flags & panel.FLAG_LONG_RUNS
     x = S.dense_vector(spec, spec.n_cols, value_dtype=vdt).astype(np.float64)
-    y, seen = _evaluate(lay, x, spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots())
+    y, seen = _evaluate(lay, x, spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds))
     assert seen == d.numel()
     ref, mag = O.spmv_f64(d.numpy(), i.numpy(), p.numpy(), (spec.n_rows, spec.n_cols), x)
     assert np.allclose(y, ref, rtol=0, atol=1e-9)
@@ -80,14 +93,51 @@ def test_layout_with_empty_rows_ragged_edges_and_duplicates(fsb_lib):
     lay = panel.build_panel_layout(d, i, p, len(lens), 10007, 16, force=True)
     assert lay is not None
     x = np.random.default_rng(6).uniform(-1, 1, 10007)
-    y, seen = _evaluate(lay, x, len(lens), 10007, fsb_lib.fsb_spmv_panel_piece_slots())
+    y, seen = _evaluate(lay, x, len(lens), 10007, fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds))
     assert seen == data.size
     ref, _ = O.spmv_f64(data, idx, ptr, (len(lens), 10007), x)
     assert np.allclose(y, ref, rtol=0, atol=1e-9)
-    # a row with more entries inside one column chunk than a piece can hold with room to spare: refused
-    data, idx, ptr = handmade_csr(7, [20, 3], 64)
-    assert panel.build_panel_layout(torch.from_numpy(data), torch.from_numpy(idx), torch.from_numpy(ptr), 2, 64, 20,
+
+
+def test_rows_with_long_runs(fsb_lib):
+    # block-structured rows: 48 consecutive columns per row, i.e. runs of up to 48 entries inside one chunk.  Such a
+    # layout is accepted, takes the largest piece and is flagged for the kernel's segmented path
+    n, width = 3000, 48
+    rng = np.random.default_rng(11)
+    start = rng.integers(0, 20000 - width, n)
+    idx = (start[:, None] + np.arange(width)[None, :]).reshape(-1).astype(np.int32)
+    ptr = (np.arange(n + 1) * width).astype(np.int32)
+    data = rng.uniform(-1, 1, idx.size).astype(np.float32)
+    d, i, p = torch.from_numpy(data), torch.from_numpy(idx), torch.from_numpy(ptr)
+    lay = panel.build_panel_layout(d, i, p, n, 20000, width, force=True)
+    assert lay is not None and lay.rounds == 16 and lay.max_run == width and lay.flags & panel.FLAG_LONG_RUNS
+    x = rng.uniform(-1, 1, 20000)
+    y, seen = _evaluate(lay, x, n, 20000, fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds))
+    assert seen == data.size
+    ref, _ = O.spmv_f64(data, idx, ptr, (n, 20000), x)
+    assert np.allclose(y, ref, rtol=0, atol=1e-9)
+    # asked for small pieces, a run of 48 still fits (a piece of 4 rounds has 128 slots)
+    lay4 = panel.build_panel_layout(d, i, p, n, 20000, width, force=True, rounds=4)
+    assert lay4 is not None and lay4.rounds == 4 and lay4.flags & panel.FLAG_LONG_RUNS
+    y4, seen4 = _evaluate(lay4, x, n, 20000, 128)
+    assert seen4 == data.size and np.allclose(y4, ref, rtol=0, atol=1e-9)
+    # a run longer than the largest piece (512 slots) cannot be laid out
+    data, idx, ptr = handmade_csr(7, [600, 3], 1024)
+    assert panel.build_panel_layout(torch.from_numpy(data), torch.from_numpy(idx), torch.from_numpy(ptr), 2, 1024, 600,
                                     force=True) is None
+    # ... but one that only outgrows the small piece moves the layout to the largest one
+    data, idx, ptr = handmade_csr(7, [200, 3], 1024)
+    lay = panel.build_panel_layout(torch.from_numpy(data), torch.from_numpy(idx), torch.from_numpy(ptr), 2, 1024, 200,
+                                   force=True, rounds=4)
+    assert lay is not None and lay.rounds == 16
+
+
+def test_choice_of_piece_size():
+    # few long runs: the smallest piece; many: the next size whose share of slow pieces stays small
+    assert panel.choose_rounds(1 << 27, [100, 0, 0]) == 4
+    assert panel.choose_rounds(1 << 27, [1 << 22, 10, 0]) == 8
+    assert panel.choose_rounds(1 << 27, [1 << 22, 1 << 21, 5]) == 16
+    assert panel.choose_rounds(1 << 27, [1 << 22, 1 << 21, 1 << 20]) == 16
 
 
 def test_selection_rules(fsb_lib):
@@ -129,7 +179,7 @@ def test_layout_with_more_x_buffers(fsb_lib, monkeypatch, n_buffers):
         assert lay is None          # eight float32 chunks of 8192 columns leave no room for the accumulators
         return
     assert lay.n_buffers == n_buffers
-    y, seen = _evaluate(lay, x.astype(np.float64), spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots())
+    y, seen = _evaluate(lay, x.astype(np.float64), spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds))
     assert seen == d.size
     ref, mag = O.spmv_f64(d, i, p, (spec.n_rows, spec.n_cols), x)
     assert O.max_bound_ratio(y, ref, mag) <= 1e-12

@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from flagsparse_b200 import synthetic as S
-from flagsparse_b200.sharded import ShardedCsrSpmv, partition_rows_by_nnz
+from flagsparse_b200.sharded import ShardedCsrSpmm, ShardedCsrSpmv, partition_rows_by_nnz, slice_plan
 
 
 def test_partition_is_balanced_and_covers():
@@ -74,7 +74,20 @@ def _worker(rank, world, port, scenario, result_dir):
         for rep in range(2):
             y = op.matvec(torch.from_numpy(x) * (rep + 1))
         full = O.spmv_base(data, idx, ptr, (spec.n_rows, spec.n_cols), x * 2)
-        np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([int(np.array_equal(y.numpy(), full))]))
+        ok = np.array_equal(y.numpy(), full)
+
+        # the same shards as a sharded SpMM: B replicated, C assembled on every rank
+        B = S.dense_vector(spec, spec.n_cols, n_dense=5)
+
+        def local_spmm(Bv, out):
+            out.copy_(torch.from_numpy(O.spmm_base(ld, li, lp, (r1 - r0, spec.n_cols), Bv.numpy())))
+
+        mm = ShardedCsrSpmm(torch.from_numpy(ld), torch.from_numpy(li), torch.from_numpy(lp), r0,
+                            (spec.n_rows, spec.n_cols), mode="nccl", local_spmm=local_spmm)
+        C = mm.matmul(torch.from_numpy(B))
+        ok = ok and C.shape == (spec.n_rows, 5) and np.array_equal(
+            C.numpy(), O.spmm_base(data, idx, ptr, (spec.n_rows, spec.n_cols), B))
+        np.save(os.path.join(result_dir, f"ok{rank}.npy"), np.array([int(ok)]))
     finally:
         dist.destroy_process_group()
 
@@ -89,3 +102,20 @@ def test_sharded_assembly_on_gloo(world, tmp_path):
 def test_inconsistent_shards_are_rejected_on_every_rank(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), "wrong_cover", str(tmp_path)), nprocs=2, join=True)
     assert all((tmp_path / f"err{r}.npy").exists() for r in range(2))
+
+
+def test_slice_plan():
+    # whole waves, later slices never larger, everything covered once
+    assert slice_plan(296, 148, 4) == [(0, 148), (148, 296)]
+    assert slice_plan(888, 148, 4) == [(0, 296), (296, 592), (592, 740), (740, 888)]
+    assert slice_plan(444, 148, 4) == [(0, 148), (148, 296), (296, 444)]
+    assert slice_plan(100, 148, 4) == [(0, 100)]
+    assert slice_plan(150, 148, 4) == [(0, 148), (148, 150)]
+    assert slice_plan(0, 148, 4) == []
+    for n in (1, 147, 149, 1000, 1776):
+        for k in (1, 2, 4):
+            plan = slice_plan(n, 148, k)
+            assert plan[0][0] == 0 and plan[-1][1] == n and len(plan) <= k
+            assert all(a[1] == b[0] for a, b in zip(plan, plan[1:]))
+            sizes = [e - b for b, e in plan]
+            assert sizes == sorted(sizes, reverse=True)

@@ -246,14 +246,17 @@ def test_analysis_statistics(cuda, fsb_lib):
 
 
 # ---- the benchmark configurations -----------------------------------------------------------------------
-@pytest.mark.parametrize("name,rows", [("c2", 1 << 17), ("c3", 1 << 19), ("c5", 1 << 17)])
+@pytest.mark.parametrize("name,rows", [("c2", 1 << 17), ("c3", 1 << 19), ("c5", 1 << 17), ("c5", 1 << 22)])
 def test_configs_reduced_full_oracle(cuda, fsb_lib, name, rows):
+    # c5 at 2^22 rows keeps the full band of +-2^20 columns: 256 column chunks per row block, a few thousand entries
+    # per unit -- the geometry of the full-size matrix on the panel kernel
     spec = S.config_spec(name).scaled(rows)
     pdt = "int64" if name == "c5" else "int32"
     d, i, p = S.generate_csr(spec, "cuda:0", indptr_dtype=pdt)
     x = S.dense_vector(spec, spec.n_cols, "cuda:0")
     dn, inn, pn, xn = d.cpu().numpy(), i.cpu().numpy(), p.cpu().numpy(), x.cpu().numpy()
-    for algo in ALGOS:
+    # the panel kernel where the columns are banded (forcing it on uniform columns would build a unit per chunk)
+    for algo in ALGOS + (["panel"] if name != "c3" else []):
         with env(FSB_SPMV_ALGO=algo):
             y = fs.flagsparse_spmv_csr(d, i, p, x, (spec.n_rows, spec.n_cols))
         assert_spmv_ok(y.cpu().numpy(), dn, inn, pn, (spec.n_rows, spec.n_cols), xn, what=f"{name}/{algo}")
@@ -302,6 +305,112 @@ def test_config_c3_full_size(cuda, fsb_lib):
     assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)
     assert int(lens.max()) > 60000
     print(f"c3: nnz {d.numel()}, longest row {int(lens.max())}, worst bound ratio {worst:.2e}")
+
+
+def test_config_c5_full_size_on_the_panel_kernel(cuda, fsb_lib):
+    """The 2^26-row matrix of the sharded configuration on one GPU, through the kernel the benchmark times on it:
+    host-regenerated row blocks (the ends, around the row where the entry count passes 2^31, random ones), the
+    wait-status word, bit equality of two calls and exact scaling."""
+    if torch.cuda.get_device_properties(0).total_memory < 80 * 2**30:
+        pytest.skip("needs about 60 GB of device memory")
+    spec = S.config_spec("c5")
+    d, i, p = S.generate_csr(spec, "cuda:0", indptr_dtype="int64")
+    assert d.numel() > 2**31 - 2**24 and p.dtype == torch.int64
+    x = S.dense_vector(spec, spec.n_cols, "cuda:0")
+    prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+    assert prep.algo == _lib.FSB_SPMV_PANEL and prep.panel is not None
+    lay = prep.panel
+    assert lay.n_units // lay.n_row_blocks > 200            # every row block spans the whole band of chunks
+    y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    prep.check_status()
+    edge = int(torch.searchsorted(p, torch.tensor([2**31 - 1], device=p.device))[0]) if d.numel() >= 2**31 else None
+    blocks = sample_blocks(spec.n_rows, 8, 2048)
+    if edge is not None:
+        blocks.append((max(0, edge - 1024), min(spec.n_rows, edge + 1024)))
+    blocks.append((lay.rb_rows - 1024, lay.rb_rows + 1024))  # across the first row-block boundary
+    worst = check_spmv_blocks(spec, y, x.cpu().numpy(), blocks, indptr_dtype="int64")
+    assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), y)
+    assert torch.equal(fs.flagsparse_spmv_csr(x=x * 2, prepared=prep), y * 2)
+    print(f"c5 panel: nnz {d.numel()}, rounds {lay.rounds}, flags {lay.flags}, longest run {lay.max_run}, "
+          f"worst bound ratio {worst:.2e}")
+
+
+def test_panel_kernel_with_long_runs(cuda, fsb_lib):
+    """Rows of 48 consecutive columns (block-structured matrices): runs longer than a lane's rounds, summed through
+    the kernel's segmented path; every piece size."""
+    n, width, n_cols = 200000, 48, 300000
+    rng = np.random.default_rng(3)
+    start = np.clip(np.arange(n) * n_cols // n + rng.integers(-2000, 2000, n), 0, n_cols - width)
+    idx = (start[:, None] + np.arange(width)[None, :]).reshape(-1).astype(np.int32)
+    ptr = (np.arange(n + 1, dtype=np.int64) * width).astype(np.int32)
+    data = rng.uniform(-1, 1, idx.size).astype(np.float32)
+    x = rng.uniform(-1, 1, n_cols).astype(np.float32)
+    from flagsparse_b200 import panel as P
+
+    for rounds in (None, 4, 8, 16):
+        with env(FSB_SPMV_ALGO="panel", FSB_PANEL_ROUNDS=rounds):
+            prep = fs.prepare_spmv_csr(dev(data), dev(idx), dev(ptr), (n, n_cols))
+        assert prep.panel is not None and prep.panel.flags & P.FLAG_LONG_RUNS and prep.panel.max_run == width
+        assert prep.panel.rounds == (rounds or 16)
+        y = fs.flagsparse_spmv_csr(x=dev(x), prepared=prep)
+        assert_spmv_ok(y.cpu().numpy(), data, idx, ptr, (n, n_cols), x, what=f"48-entry runs, rounds {rounds}")
+        assert torch.equal(fs.flagsparse_spmv_csr(x=dev(x), prepared=prep), y)
+        prep.check_status()
+
+
+@pytest.mark.parametrize("rounds", [4, 8, 16])
+@pytest.mark.parametrize("vdt", ["float32", "float64"])
+def test_panel_piece_sizes(cuda, fsb_lib, rounds, vdt):
+    spec = S.config_spec("c5").scaled(1 << 20)
+    d, i, p = S.generate_csr(spec, "cuda:0", value_dtype=vdt)
+    x = S.dense_vector(spec, spec.n_cols, "cuda:0", value_dtype=vdt)
+    with env(FSB_SPMV_ALGO="panel", FSB_PANEL_ROUNDS=rounds):
+        prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+    assert prep.panel.rounds == rounds
+    y = fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    assert_spmv_ok(y.cpu().numpy(), d.cpu().numpy(), i.cpu().numpy(), p.cpu().numpy(), (spec.n_rows, spec.n_cols),
+                   x.cpu().numpy(), what=f"panel rounds {rounds} {vdt}")
+    prep.check_status()
+    # the same product launched in three slices of row blocks (what the sharded driver does)
+    from flagsparse_b200 import panel as P
+    from flagsparse_b200._common import _stream_ptr
+
+    y2 = torch.full_like(y, float("nan"))
+    nb = prep.panel.n_row_blocks
+    for b0, b1 in ((0, nb // 3), (nb // 3, nb // 3), (nb // 3, nb)):
+        P.launch_panel(prep.panel, x, y2, spec.n_rows, spec.n_cols, _stream_ptr(x.device), b0, b1)
+    assert torch.equal(y2, y)
+
+
+def test_a_wait_that_runs_out_is_reported_to_the_caller(cuda, fsb_lib):
+    """The kernel's bounded wait on a copy of x, made to run out (the kernel is told to expect 16 bytes that never
+    arrive and to give up after a short spin): it returns, sets its status word, and the next look at the prepared
+    matrix raises instead of handing on an incomplete y.  Nothing faults and nothing hangs; the following product is
+    correct again."""
+    from flagsparse_b200 import panel as P
+
+    spec = S.config_spec("c2").scaled(1 << 17)
+    d, i, p = S.generate_csr(spec, "cuda:0")
+    x = S.dense_vector(spec, spec.n_cols, "cuda:0")
+    with env(FSB_SPMV_ALGO="panel"):
+        prep = fs.prepare_spmv_csr(d, i, p, (spec.n_rows, spec.n_cols))
+    good = fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    prep.check_status()
+    prep.panel.flags |= P.FLAG_DEBUG_TIMEOUT
+    fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        prep.check_status()
+    assert int(prep.panel.status.item()) == 0               # the word was reset
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        fs.flagsparse_spmv_csr(x=x, prepared=prep, return_time=True)
+    # the failure is also seen, without any wait, by the next product on the same matrix
+    fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    torch.cuda.synchronize()
+    prep.panel.flags &= ~P.FLAG_DEBUG_TIMEOUT
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        fs.flagsparse_spmv_csr(x=x, prepared=prep)
+    assert torch.equal(fs.flagsparse_spmv_csr(x=x, prepared=prep), good)
+    prep.check_status()
 
 
 def test_more_than_2_31_entries(cuda, fsb_lib):
