@@ -90,14 +90,18 @@ def _tile_plan(indptr, n_rows, nnz, tile_nnz):
 
 
 class StatusWord:
-    """The device word through which a kernel reports that one of its bounded waits ran out, and the host side of
-    it.  After each launch the word is copied to pinned host memory behind an event; the next call on the same
-    object (or an explicit check()) looks at the copy once the event has passed, resets the word and raises, so a
-    product whose kernel gave up is never handed on silently."""
+    """The word through which a kernel reports that one of its bounded waits ran out, and the host side of it.
+    The word lives in pinned host memory that the GPU writes directly (only when a wait does run out), so looking
+    at it costs neither a copy nor a synchronisation: every call on the same object polls it, and check() waits
+    for the last launch first.  A set word is reset and turned into a RuntimeError, so a product whose kernel gave
+    up is never handed on silently."""
 
     def __init__(self, device):
-        self.word = torch.zeros(1, dtype=torch.int32, device=device)
-        self._host = None
+        device = torch.device(device)
+        self._cuda = device.type == "cuda"
+        self.word = torch.zeros(1, dtype=torch.int32)
+        if self._cuda:
+            self.word = self.word.pin_memory()       # page-locked: the same address is valid on the device
         self._event = None
         self._what = None
 
@@ -105,40 +109,32 @@ class StatusWord:
         return self.word.data_ptr()
 
     def item(self):
-        return int(self.word.item())
+        return int(self.word[0])
 
     def posted(self, what, stream=None):
         """Call right after a launch that may set the word; `stream` is the torch stream of that launch (default:
         the current one)."""
-        if not self.word.is_cuda:
+        if not self._cuda:
             return
-        if self._host is None:
-            self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        if self._event is None:
             self._event = torch.cuda.Event()
-        stream = stream or torch.cuda.current_stream(self.word.device)
-        with torch.cuda.stream(stream):
-            self._host.copy_(self.word, non_blocking=True)
-        self._event.record(stream)
+        self._event.record(stream or torch.cuda.current_stream())
         self._what = what
 
     def poll(self):
-        """Raise if an earlier launch is known to have failed; never waits for the GPU."""
-        if self._what is None or not self._event.query():
-            return
-        self._raise_if_set()
+        """Raise if a launch is known to have failed; never waits for the GPU."""
+        if int(self.word[0]) != 0:
+            self._raise()
 
     def check(self):
-        """Wait for the last launch and raise if it failed."""
-        if self._what is None:
-            return
-        self._event.synchronize()
-        self._raise_if_set()
+        """Wait for the last launch and raise if it (or an earlier one) failed."""
+        if self._event is not None:
+            self._event.synchronize()
+        if int(self.word[0]) != 0:
+            self._raise()
 
-    def _raise_if_set(self):
-        what, code = self._what, int(self._host[0])
-        self._what = None
-        if code != 0:
-            self.word.zero_()
-            self._host.zero_()
-            raise RuntimeError(f"{what}: a device-side wait ran out (status {code}); the result of that call is "
-                               "incomplete")
+    def _raise(self):
+        code, what = int(self.word[0]), self._what or "a kernel of this matrix"
+        self.word.zero_()
+        raise RuntimeError(f"{what}: a device-side wait ran out (status {code}); the result of that call is "
+                           "incomplete")

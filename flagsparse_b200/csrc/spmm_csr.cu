@@ -127,7 +127,7 @@ spmm_tile_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P*
     __syncthreads();
     if (bulk && s_failed) {
       // the copy did not land within the bound: report it and leave this tile unwritten
-      if (tid == 0 && status != nullptr) atomicExch(status, 1);
+      if (tid == 0 && status != nullptr) *reinterpret_cast<volatile int32_t*>(status) = 1;  // may be host memory
       mbar_wait_bounded(&s_bar, 0);  // one more bounded wait so that no copy is in flight at exit
       return;
     }

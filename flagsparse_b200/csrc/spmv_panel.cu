@@ -13,15 +13,16 @@
 //   - the CW elements of x a unit needs arrive in shared memory by a cp.async.bulk copy (mbarrier
 //     completion), n_buffers - 1 units ahead of their use;
 //   - a warp takes a whole piece: lane l owns slots R*l .. R*l+R-1 (stored interleaved so that each 128-bit
-//     load of the warp is contiguous).  In round k every lane handles its k-th slot and keeps the running sum
-//     of its current row in a register; when the row ends it adds the sum to the row's accumulator in shared
-//     memory.  A row with at most R entries in the unit touches at most two lanes and ends in them in
-//     different rounds, so the 32 lanes of a round always add into 32 different accumulators: no shuffles, no
-//     atomics.  Layouts that hold longer runs say so (FSB_PANEL_LONG_RUNS); for them the add of a lane's last
-//     slot goes through a segmented warp reduction whenever two neighbouring lanes end on the same row;
+//     load of the warp is contiguous).  In round k every lane handles its k-th slot: value * x[column] is added
+//     to the row's accumulator in shared memory.  Two slots of one round are R positions apart and a row has at
+//     most R entries in the unit, so the 32 lanes of a round always add into 32 different accumulators: no
+//     shuffles, no atomics, no predicates.  Where rows have several entries per unit (FSB_PANEL_RUNS) a lane
+//     instead sums a row's products in a register and adds the sum when the row ends; layouts that hold runs
+//     longer than R say so (FSB_PANEL_LONG_RUNS), and a lane's last slot then goes through a segmented warp
+//     reduction whenever two neighbouring lanes end on the same row;
 //   - the pieces of the CTA are dealt to its warps round-robin across unit boundaries, and every warp keeps
-//     the next few 4-slot groups of its own pieces in flight (a register ring), whichever unit they belong
-//     to: a unit with only a few pieces costs no trip to DRAM of its own;
+//     the next group of slots of its own pieces in flight, whichever unit it belongs to: a unit with only a
+//     few pieces costs no trip to DRAM of its own;
 //   - rounds follow each other in program order, a row lives in one piece per unit, and units are separated
 //     by a CTA barrier, so every accumulator receives its terms in one fixed order: bit-reproducible;
 //   - after the last unit the accumulators are written to y, each row exactly once.
@@ -33,7 +34,6 @@ constexpr int kPanelWarps = 32;
 constexpr int kPanelThreads = kPanelWarps * 32;
 constexpr int kPanelWaitSpins = 1 << 22;
 constexpr int kPanelWaitSpinsDebug = 1 << 10;   // FSB_PANEL_DEBUG_TIMEOUT: give up quickly
-constexpr uint32_t kNoRow = 0xFFFFu;
 
 __device__ __forceinline__ uint32_t p_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void p_mbar_init(uint64_t* bar, int count) {
@@ -59,54 +59,82 @@ __device__ __forceinline__ bool p_wait_bounded(uint64_t* bar, uint32_t phase, in
   return false;
 }
 
-// Four consecutive slots of one lane: rounds 4g .. 4g+3 of a piece.
-template <typename V>
+// G consecutive slots of one lane (G = 4 or 8): rounds G*g .. G*g+G-1 of a piece.
+template <typename V, int G>
 struct Group {
-  V v[4];
-  uint32_t w[4];
+  V v[G];
+  uint32_t w[G];
 };
 
 // Storage inside a piece of 32 * R slots: slot (lane, k), k = 0..R-1, of the value array sits at
 // (k / E) * 32 * E + lane * E + k % E with E = elements per 16 bytes, and of the packed-word array at
 // (k / 4) * 128 + lane * 4 + k % 4, so that every 128-bit load of a warp reads 512 contiguous bytes.
-__device__ __forceinline__ void ld_group(const float* piece_val, const uint32_t* piece_rc, int lane, int g,
-                                         Group<float>& out) {
-  ld_stream4(piece_val + g * 128 + lane * 4, out.v);
-  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece_rc + g * 128 + lane * 4));
-  out.w[0] = t.x; out.w[1] = t.y; out.w[2] = t.z; out.w[3] = t.w;
+// slots 4q .. 4q+3 of a lane (q-th 128-bit quad of the piece)
+__device__ __forceinline__ void ld_quad(const float* piece_val, int lane, int q, float* v) {
+  const float4 t = __ldcs(reinterpret_cast<const float4*>(piece_val + q * 128 + lane * 4));
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
 }
-__device__ __forceinline__ void ld_group(const double* piece_val, const uint32_t* piece_rc, int lane, int g,
-                                         Group<double>& out) {
-  const double2 a = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * g) * 64 + lane * 2));
-  const double2 b = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * g + 1) * 64 + lane * 2));
-  out.v[0] = a.x; out.v[1] = a.y; out.v[2] = b.x; out.v[3] = b.y;
-  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece_rc + g * 128 + lane * 4));
-  out.w[0] = t.x; out.w[1] = t.y; out.w[2] = t.z; out.w[3] = t.w;
+__device__ __forceinline__ void ld_quad(const double* piece_val, int lane, int q, double* v) {
+  const double2 a = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * q) * 64 + lane * 2));
+  const double2 b = __ldcs(reinterpret_cast<const double2*>(piece_val + (2 * q + 1) * 64 + lane * 2));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void ld_quad(const uint32_t* piece_rc, int lane, int q, uint32_t* w) {
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(piece_rc + q * 128 + lane * 4));
+  w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+}
+template <typename V, int G>
+__device__ __forceinline__ void ld_group(const V* piece_val, const uint32_t* piece_rc, int lane, int g,
+                                         Group<V, G>& out) {
+#pragma unroll
+  for (int j = 0; j < G / 4; ++j) {
+    ld_quad(piece_val, lane, g * (G / 4) + j, &out.v[4 * j]);
+    ld_quad(piece_rc, lane, g * (G / 4) + j, &out.w[4 * j]);
+  }
 }
 
-// The four rounds of one group.  Products of one row are summed in a register and added to the row's
-// accumulator when the row ends (next_word is the lane's next slot, or a kNoRow word after its last one).
-//   LAST   this is the lane's last group of the piece: its fourth slot closes whatever row is open (a constant
-//          once the caller's loops are unrolled)
-//   CHECK  the layout may hold rows with more than R entries in a unit: such a row covers whole lanes, which
-//          all close it with their last slot, i.e. in the same round; those sums are combined by a segmented
-//          scan over the lanes (fixed order) and added once
-template <typename V, bool CHECK>
-__device__ __forceinline__ void panel_rounds4(const Group<V>& G, uint32_t next_word, const bool LAST, V& acc,
-                                              const V* __restrict__ xs, V* __restrict__ y_part, int lane) {
+// The G rounds of one group, for layouts in which no row has more entries in a unit than a lane has rounds
+// (every round then finds its 32 lanes on 32 different accumulators): each slot adds its product straight into
+// its row's accumulator.  Unused slots carry value 0 and the index of a spare accumulator, so nothing is
+// predicated and the warp stays converged; rounds follow each other in program order.
+template <typename V, int GS>
+__device__ __forceinline__ void panel_rounds_direct(const Group<V, GS>& G, const V* __restrict__ xs,
+                                                    V* __restrict__ y_part) {
   // x does not change during a unit: the gathers go out first, so that their latencies overlap instead of
   // queueing behind the per-round ordering points below
-  V p[4];
+  V xv[GS];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) p[k] = G.v[k] * xs[G.w[k] & 0xFFFFu];   // padding slots: value 0, column 0
+  for (int k = 0; k < GS; ++k) xv[k] = xs[G.w[k] & 0xFFFFu];
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
+  for (int k = 0; k < GS; ++k) {
     const uint32_t row = G.w[k] >> 16;
-    const uint32_t next_row = (k < 3 ? G.w[k + 1] : next_word) >> 16;
-    const bool live = row != kNoRow;
+    y_part[row] = fma(G.v[k], xv[k], y_part[row]);
+    __syncwarp();  // orders this round's accumulator updates before the next round's
+  }
+}
+
+// The G rounds of one group, for layouts whose rows mostly have several entries per unit (FSB_PANEL_RUNS).
+// Products of one row are summed in a register and added to the row's accumulator when the row ends (next_word
+// is the lane's next slot, or a word of the spare accumulator after its last one): one trip to shared memory
+// per run instead of one per entry.  CLASH (layouts flagged FSB_PANEL_LONG_RUNS): a row with more than R
+// entries in the unit covers whole lanes, which all close it with their last slot, i.e. in the same round;
+// those sums are combined by a segmented scan over the lanes (fixed order) and added once.
+//   LAST   this is the lane's last group of the piece (a constant once the caller's loops are unrolled)
+template <typename V, int GS, bool CLASH>
+__device__ __forceinline__ void panel_rounds_runs(const Group<V, GS>& G, uint32_t next_word, const bool LAST, V& acc,
+                                                  const V* __restrict__ xs, V* __restrict__ y_part, int lane,
+                                                  uint32_t pad_row) {
+  V p[GS];
+#pragma unroll
+  for (int k = 0; k < GS; ++k) p[k] = G.v[k] * xs[G.w[k] & 0xFFFFu];   // unused slots: value 0, column 0
+#pragma unroll
+  for (int k = 0; k < GS; ++k) {
+    const uint32_t row = G.w[k] >> 16;
+    const uint32_t next_row = (k < GS - 1 ? G.w[k + 1] : next_word) >> 16;
+    const bool live = row != pad_row;
     if (live) acc += p[k];
     const bool flush = live && next_row != row;
-    if (CHECK && LAST && k == 3) {
+    if (CLASH && LAST && k == GS - 1) {
       const uint32_t row_up = __shfl_down_sync(0xffffffffu, row, 1);
       const bool clash = flush && lane < 31 && row_up == row;
       if (__any_sync(0xffffffffu, clash)) {
@@ -132,6 +160,7 @@ __device__ __forceinline__ void panel_rounds4(const Group<V>& G, uint32_t next_w
   }
 }
 
+constexpr int kModeDirect = 0, kModeRuns = 1, kModeRunsClash = 2;
 constexpr int kMaxXBuffers = 8;
 constexpr int kUnitWindow = 512;   // units whose tables are kept in shared memory at a time
 constexpr int kUnitLookahead = kMaxXBuffers;
@@ -152,22 +181,22 @@ struct PanelGeom {
   int chunk_cols;
   int n_buf;
   int debug;      // FSB_PANEL_DEBUG_TIMEOUT: the first chunk's barrier expects bytes that never come
+  uint32_t pad_row;  // accumulator index carried by unused slots (one past the CTA's real accumulators)
 };
 
 // Units u0 .. u1-1 of one CTA, in order: chunk of x in, pieces added into y_part.  Returns false when a bounded
 // wait ran out (every thread of the CTA gets the same answer).
 //   - x chunks are fetched n_buf - 1 units ahead into n_buf buffers (unit number `ord` of the CTA uses buffer
 //     ord % n_buf; the packed word of a slot already holds buffer * chunk_cols + local column);
-//   - piece p goes to warp (p - first piece of the CTA) % 32; the warp's groups form one stream q = 0, 1, ...
-//     (group q % (R/4) of its piece number q / (R/4)) of which D are held in a register ring: group q + D is
-//     requested as soon as group q has been consumed.
-template <typename V, int R, int D, bool CHECK>
+//   - piece p goes to warp (p - first piece of the CTA) % 32; a warp walks its pieces in groups of G slots per
+//     lane (group q % (R/G) of its piece number q / (R/G)) and always has the next group on its way.
+template <typename V, int R, int G, int MODE>
 __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const uint32_t* __restrict__ rc,
                                                 const int32_t* __restrict__ unit_piece_ptr,
                                                 const int32_t* __restrict__ unit_chunk, int u0, int u1,
                                                 const V* __restrict__ x, const PanelGeom& gm,
                                                 const PanelShared<V>& sh) {
-  constexpr int GPP = R / 4;          // groups per piece
+  constexpr int GPP = R / G;          // groups per piece
   constexpr int SLOTS = 32 * R;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunk_cols = gm.chunk_cols, n_buf = gm.n_buf;
@@ -196,74 +225,100 @@ __device__ __forceinline__ bool panel_run_units(const V* __restrict__ val, const
 
   const int p_first = unit_piece_ptr[u0];
   const int p_cta_end = unit_piece_ptr[u1];
+  int pc = p_first + warp;            // this warp's next piece
+  // The entries do not depend on x: the warp's first group(s) are requested before anything else.
+  //   RING   two groups in a register ring, refilled as soon as a group has been consumed (the request for
+  //          group q + 2 leaves after group q); measured best where every slot costs a trip to an accumulator
+  //   else   the next group is requested right before the current one is used, into registers that are dead
+  //          otherwise; measured best for the run-summing rounds, which need the registers themselves
+  constexpr bool RING = MODE == kModeDirect;
   const int n_my = (p_cta_end - p_first - warp + kPanelWarps - 1) / kPanelWarps;   // pieces of this warp (may be <= 0)
   const int n_groups = n_my > 0 ? n_my * GPP : 0;
-  Group<V> ring[D];
-  auto request = [&](int q, Group<V>& slot) {
+  Group<V, G> ring[2];
+  auto request = [&](int q, Group<V, G>& slot) {
     if (q < n_groups) {
       const size_t piece = (size_t)(p_first + warp + kPanelWarps * (q / GPP));
       ld_group(val + piece * SLOTS, rc + piece * SLOTS, lane, q % GPP, slot);
     }
   };
-  // the entries do not depend on x: the first D groups of the warp are requested before anything else
-#pragma unroll
-  for (int i = 0; i < D; ++i) request(i, ring[i]);
   int q = 0, phase = 0;
-  int pc = p_first + warp;            // this warp's next piece
+  if (RING) {
+    request(0, ring[0]);
+    request(1, ring[1]);
+  } else if (pc < p_cta_end) {
+    ld_group(val + (size_t)pc * SLOTS, rc + (size_t)pc * SLOTS, lane, 0, ring[0]);
+  }
 
-  // chunks of the first n_buf - 1 units
-  bool plain = false;  // some chunk was written with ordinary stores: needs a CTA barrier before its first use
-  for (int a = 0; a < n_buf - 1 && u0 + a < u1; ++a) plain |= load_chunk(unit_chunk[u0 + a], a, a == 0);
+  // chunks of the first n_buf - 1 units (a chunk written with ordinary stores is also at least one CTA barrier
+  // ahead of its first use)
+  for (int a = 0; a < n_buf - 1 && u0 + a < u1; ++a) load_chunk(unit_chunk[u0 + a], a, a == 0);
 
   int b = 0, par = 0;                  // buffer and barrier parity of the current unit
+  // One thread waits for a chunk of x; the CTA barrier that follows hands what it has seen on to everybody
+  // (1023 threads polling the same mbarrier cost more issue slots than the products themselves).
+  if (tid == 0 && !p_wait_bounded(&bars[0], 0u, spins)) *sh.failed = 1;
   for (int w0 = u0; w0 < u1; w0 += kUnitWindow) {
     const int nwin = (u1 - w0) < kUnitWindow ? (u1 - w0) : kUnitWindow;
     const int nch = (u1 - w0) < (kUnitWindow + kUnitLookahead) ? (u1 - w0) : (kUnitWindow + kUnitLookahead);
     if (w0 > u0) __syncthreads();  // the previous window's tables are no longer read
     for (int i = tid; i <= nwin; i += kPanelThreads) sh.upp[i] = unit_piece_ptr[w0 + i];
     for (int i = tid; i < nch; i += kPanelThreads) sh.uch[i] = unit_chunk[w0 + i];
-    __syncthreads();
+    __syncthreads();               // also: the first chunk has landed (or the wait for it was given up)
     for (int u = w0; u < w0 + nwin; ++u) {
-      // the buffer of the previous unit was last read before the barrier that closed it: free to refill
-      if (u + n_buf - 1 < u1) {
-        int bn = b + n_buf - 1;
-        bn = bn >= n_buf ? bn - n_buf : bn;
-        plain |= load_chunk(sh.uch[u + n_buf - 1 - w0], bn, u == u0 && n_buf == 1);
-      }
-      const int p_end = sh.upp[u - w0 + 1];
-      if (!p_wait_bounded(&bars[b], (uint32_t)par, spins)) *sh.failed = 1;
-      if (plain && u == u0) __syncthreads();  // later plain chunks are written at least one unit (barrier) ahead
-      while (pc < p_end) {
-        V acc = (V)0;
-#pragma unroll
-        for (int g = 0; g < GPP; ++g) {
-#pragma unroll
-          for (int i = 0; i < D; ++i) {
-            if (phase == i) {
-              // a lane's run ends with its last slot of the piece; inside the piece the next group tells
-              const uint32_t next_word = (g + 1 < GPP) ? ring[(i + 1) % D].w[0] : (kNoRow << 16);
-              panel_rounds4<V, CHECK>(ring[i], next_word, g + 1 == GPP, acc, xs, y_part, lane);
-              request(q + D, ring[i]);
-            }
-          }
-          phase = (phase + 1 == D) ? 0 : phase + 1;
-          ++q;
-        }
-        pc += kPanelWarps;
-      }
-      __syncthreads();  // every add of this unit is done; its x buffer may be refilled
       if (*sh.failed) {
         // leave no copy in flight into this CTA's shared memory: one more bounded wait per chunk requested ahead
         int bb = b, pp = par;
-        for (int a = 1; a < n_buf && u + a < u1; ++a) {
+        for (int a = 1; a < n_buf - 1 && u + a < u1; ++a) {
           if (++bb == n_buf) { bb = 0; pp ^= 1; }
           p_wait_bounded(&bars[bb], (uint32_t)pp, spins);
         }
         return false;
       }
+      // the buffer of the previous unit was last read before the barrier that closed it: free to refill
+      if (u + n_buf - 1 < u1) {
+        int bn = b + n_buf - 1;
+        bn = bn >= n_buf ? bn - n_buf : bn;
+        load_chunk(sh.uch[u + n_buf - 1 - w0], bn, false);
+      }
+      const int p_end = sh.upp[u - w0 + 1];
+      while (pc < p_end) {
+        V acc = (V)0;
+#pragma unroll
+        for (int g = 0; g < GPP; ++g) {
+          if (RING) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              if (phase == i) {
+                panel_rounds_direct<V, G>(ring[i], xs, y_part);
+                request(q + 2, ring[i]);
+              }
+            }
+            phase ^= 1;
+            ++q;
+          } else {
+            // the next group (of this piece, or the first one of this warp's next piece, whichever unit that
+            // piece belongs to) is in flight while this one is used
+            Group<V, G> nxt;
+            const bool more = g + 1 < GPP;
+            const int np = more ? pc : pc + kPanelWarps;
+            const bool have = np < p_cta_end;
+            if (have) ld_group(val + (size_t)np * SLOTS, rc + (size_t)np * SLOTS, lane, more ? g + 1 : 0, nxt);
+            // a lane's run ends with its last slot of the piece; inside the piece the next group tells
+            const uint32_t next_word = more ? nxt.w[0] : (gm.pad_row << 16);
+            panel_rounds_runs<V, G, MODE == kModeRunsClash>(ring[0], next_word, !more, acc, xs, y_part, lane,
+                                                             gm.pad_row);
+            if (have) ring[0] = nxt;
+          }
+        }
+        pc += kPanelWarps;
+      }
       if (++b == n_buf) { b = 0; par ^= 1; }
+      // the next unit's chunk must have landed before anybody gathers from it
+      if (tid == 0 && u + 1 < u1 && !p_wait_bounded(&bars[b], (uint32_t)par, spins)) *sh.failed = 1;
+      __syncthreads();  // every add of this unit is done (its x buffer may be refilled); the next chunk is in
     }
   }
+  if (*sh.failed) return false;
   return true;
 }
 
@@ -276,7 +331,7 @@ struct PanelStatic {
 
 template <typename V>
 __device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* smem, PanelStatic* st, int chunk_cols,
-                                            int n_buf, int n_acc) {
+                                            int n_buf, int n_acc, uint32_t pad_row) {
   sh.xs = reinterpret_cast<V*>(smem);
   sh.y_part = sh.xs + (size_t)n_buf * chunk_cols;
   sh.bars = st->bars;
@@ -287,6 +342,7 @@ __device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* s
   for (int i = tid; i < n_acc; i += kPanelThreads) sh.y_part[i] = (V)0;
   if (tid == 0) {
     st->failed = 0;
+    sh.y_part[pad_row] = (V)0;
     for (int b = 0; b < n_buf; ++b) p_mbar_init(&st->bars[b], 1);
     p_fence_init();
   }
@@ -295,7 +351,7 @@ __device__ __forceinline__ void panel_setup(PanelShared<V>& sh, unsigned char* s
 
 // One CTA per block of rb_rows consecutive rows (block block_begin + blockIdx.x); every row of y the launch
 // covers is written exactly once.
-template <typename V, int R, int D, bool CHECK>
+template <typename V, int R, int G, int MODE>
 __global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, const int32_t* __restrict__ unit_piece_ptr,
                   const int32_t* __restrict__ unit_chunk, const int32_t* __restrict__ rb_unit_ptr,
@@ -308,10 +364,10 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
   const int64_t r0 = (int64_t)rb * rb_rows;
   const int nr = (int)((n_rows - r0) < (int64_t)rb_rows ? (n_rows - r0) : (int64_t)rb_rows);
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, nr);
-  if (!panel_run_units<V, R, D, CHECK>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x,
+  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, nr, gm.pad_row);
+  if (!panel_run_units<V, R, G, MODE>(val, rc, unit_piece_ptr, unit_chunk, rb_unit_ptr[rb], rb_unit_ptr[rb + 1], x,
                                        gm, sh)) {
-    if (tid == 0 && status != nullptr) atomicExch(status, 2);
+    if (tid == 0 && status != nullptr) *reinterpret_cast<volatile int32_t*>(status) = 2;  // may be host memory
     return;
   }
   // the accumulators start on a 16-byte boundary of shared memory; so does y + r0 when rb_rows is a multiple of 4
@@ -335,7 +391,7 @@ spmv_panel_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc, co
 // unit" still holds).  The units of a group are dealt to several CTAs by column range, so a CTA ends with
 // partial sums of its group's rows: it writes them to part[cta_part_ptr[cta] + (q - first q of the group)],
 // and panel_group_reduce_kernel adds the partial sums of each row in CTA order.
-template <typename V, int R, int D, bool CHECK>
+template <typename V, int R, int G, int MODE>
 __global__ void __launch_bounds__(kPanelThreads, 1)
 spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__ rc,
                          const int32_t* __restrict__ unit_piece_ptr, const int32_t* __restrict__ unit_chunk,
@@ -352,10 +408,10 @@ spmv_panel_groups_kernel(const V* __restrict__ val, const uint32_t* __restrict__
   const int vb0 = vbase[q0];
   const int n_acc = vbase[q1] - vb0;
   PanelShared<V> sh;
-  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, n_acc);
-  if (!panel_run_units<V, R, D, CHECK>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1],
+  panel_setup<V>(sh, p_smem, &p_static, gm.chunk_cols, gm.n_buf, n_acc, gm.pad_row);
+  if (!panel_run_units<V, R, G, MODE>(val, rc, unit_piece_ptr, unit_chunk, cta_unit_ptr[cta], cta_unit_ptr[cta + 1],
                                        x, gm, sh)) {
-    if (tid == 0 && status != nullptr) atomicExch(status, 2);
+    if (tid == 0 && status != nullptr) *reinterpret_cast<volatile int32_t*>(status) = 2;  // may be host memory
     return;
   }
   V* out = part + cta_part_ptr[cta];
@@ -383,9 +439,11 @@ panel_group_reduce_kernel(const V* __restrict__ part, const int32_t* __restrict_
   y[long_rows[q]] = (V)s;
 }
 
-// groups of a warp held in flight: as many as the register file allows with 1024 threads per CTA
-template <typename V> struct Depth { static constexpr int value = 4; };
-template <> struct Depth<double> { static constexpr int value = 2; };
+// Slots per group by value type and piece size.  float32: 8-slot groups (eight gathers of x leave together)
+// except for the 4-round pieces; float64: 4-slot groups.  Two groups live in registers (the one being consumed and
+// the next); with 1024 threads per CTA and 64 registers per thread, deeper prefetch measured slower.
+template <typename V, int R> struct Shape { static constexpr int G = R >= 8 ? 8 : 4; };
+template <int R> struct Shape<double, R> { static constexpr int G = 4; };
 
 }  // namespace fsb
 
@@ -397,7 +455,8 @@ extern "C" int fsb_spmv_panel_piece_slots(int rounds) {
 
 extern "C" size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers) {
   const size_t sv = vtype == FSB_F32 ? 4 : 8;
-  return (size_t)n_buffers * (size_t)chunk_cols * sv + (((size_t)rb_rows + 3) & ~(size_t)3) * sv;
+  // the accumulators of the CTA plus the spare one that unused slots add their zeros to
+  return (size_t)n_buffers * (size_t)chunk_cols * sv + (((size_t)rb_rows + 1 + 3) & ~(size_t)3) * sv;
 }
 
 extern "C" size_t fsb_spmv_panel_static_smem_bytes(void) { return sizeof(PanelStatic); }
@@ -406,17 +465,18 @@ static bool panel_buffers_ok(int n_buffers, int chunk_cols) {
   return n_buffers >= 2 && n_buffers <= kMaxXBuffers && (int64_t)n_buffers * chunk_cols <= 65536;
 }
 
-// FN<V, R, D, CHECK> for the runtime (vtype, rounds, long-runs flag)
-#define FSB_PANEL_DISPATCH(FN, V, LAUNCH)                                              \
-  do {                                                                                 \
-    constexpr int D_ = Depth<V>::value;                                                \
-    if (rounds == 4) {                                                                 \
-      if (check) LAUNCH((FN<V, 4, D_, true>)); else LAUNCH((FN<V, 4, D_, false>));     \
-    } else if (rounds == 8) {                                                          \
-      if (check) LAUNCH((FN<V, 8, D_, true>)); else LAUNCH((FN<V, 8, D_, false>));     \
-    } else {                                                                           \
-      if (check) LAUNCH((FN<V, 16, D_, true>)); else LAUNCH((FN<V, 16, D_, false>));   \
-    }                                                                                  \
+// FN<V, R, G, MODE> for the runtime (vtype, rounds, mode)
+#define FSB_PANEL_CASE(FN, V, R_, LAUNCH)                                                        \
+  do {                                                                                           \
+    if (mode == kModeRunsClash) LAUNCH((FN<V, R_, Shape<V, R_>::G, kModeRunsClash>));            \
+    else if (mode == kModeRuns) LAUNCH((FN<V, R_, Shape<V, R_>::G, kModeRuns>));                 \
+    else LAUNCH((FN<V, R_, Shape<V, R_>::G, kModeDirect>));                                      \
+  } while (0)
+#define FSB_PANEL_DISPATCH(FN, V, LAUNCH)                                                        \
+  do {                                                                                           \
+    if (rounds == 4) FSB_PANEL_CASE(FN, V, 4, LAUNCH);                                           \
+    else if (rounds == 8) FSB_PANEL_CASE(FN, V, 8, LAUNCH);                                      \
+    else FSB_PANEL_CASE(FN, V, 16, LAUNCH);                                                      \
   } while (0)
 
 extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int32_t* unit_piece_ptr,
@@ -437,8 +497,8 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
-  const bool check = (flags & FSB_PANEL_LONG_RUNS) != 0;
-  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0};
+  const int mode = (flags & FSB_PANEL_LONG_RUNS) ? kModeRunsClash : ((flags & FSB_PANEL_RUNS) ? kModeRuns : kModeDirect);
+  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0, (uint32_t)rb_rows};
   const unsigned grid = (unsigned)(block_end - block_begin);
 #define FSB_PANEL_LAUNCH_(K)                                                                                    \
   do {                                                                                                          \
@@ -480,8 +540,9 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
-  const bool check = (flags & FSB_PANEL_LONG_RUNS) != 0;
-  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0};
+  const int mode = (flags & FSB_PANEL_LONG_RUNS) ? kModeRunsClash : ((flags & FSB_PANEL_RUNS) ? kModeRuns : kModeDirect);
+  const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0,
+                     (uint32_t)max_group_acc};
   const unsigned rgrid = (unsigned)((n_long + 255) / 256);
 #define FSB_GROUPS_LAUNCH_(K)                                                                                    \
   do {                                                                                                           \

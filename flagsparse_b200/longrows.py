@@ -40,7 +40,7 @@ ACC_CAP = None              # accumulators per group; None = what fits in shared
 class LongRowLayout:
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "cta_unit_ptr", "cta_group", "group_q_ptr",
                  "group_cta_ptr", "vbase", "q_group", "long_rows", "cta_part_ptr", "part", "n_ctas", "n_groups",
-                 "n_long", "chunk_cols", "n_buffers", "rounds", "flags", "max_group_acc", "n_units", "n_pieces", "nnz",
+                 "n_long", "chunk_cols", "n_buffers", "rounds", "flags", "max_group_acc", "pad_row", "n_units", "n_pieces", "nnz",
                  "x_overhead", "slot_overhead", "status")
 
     def nbytes(self):
@@ -193,11 +193,11 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     acc_p = vrow_p - group_vb[q_group[q_p]]
     del q_p, sub_p
     packed = _panel.pack_pieces(data[src[perm]], acc_p, cols[perm], vrow_p, unit_of_entry, ustart, u_ord, CW, rounds,
-                                None, n_buffers=NB)
+                                None, n_buffers=NB, pad_row=max_group_acc)
     del acc_p, vrow_p, unit_of_entry, src, cols, perm
     if packed is None:
         return None
-    val, rc, upiece, n_pieces, max_run = packed
+    val, rc, upiece, n_pieces, max_run, n_runs = packed
 
     lay = LongRowLayout()
     lay.val, lay.rc = val, rc
@@ -210,7 +210,10 @@ def build_long_row_layout(data, indices, indptr, lens, is_long, n_cols, n_ctas_t
     lay.part = torch.zeros(max(1, int(cta_part_ptr[-1].item())), dtype=data.dtype, device=dev)
     lay.n_ctas, lay.n_groups, lay.n_long = n_ctas, n_groups, n_long
     lay.chunk_cols, lay.n_buffers, lay.max_group_acc = CW, NB, max_group_acc
-    lay.rounds, lay.flags = rounds, (_panel.FLAG_LONG_RUNS if max_run > rounds else 0)
+    lay.pad_row = max_group_acc
+    lay.rounds = rounds
+    lay.flags = (_panel.FLAG_LONG_RUNS if max_run > rounds else 0) | (
+        _panel.FLAG_RUNS if nnz >= _panel.RUNS_MIN_MEAN * n_runs else 0)
     lay.n_units, lay.n_pieces, lay.nnz = n_units, n_pieces, nnz
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)

@@ -25,22 +25,21 @@ MAX_X_OVERHEAD_F64 = 0.8
 MAX_SLOT_OVERHEAD = 1.25    # slots stored / entries
 N_BUFFERS = 2               # chunks of x in shared memory (fetched N_BUFFERS - 1 units ahead)
 ROUNDS = (4, 8, 16)         # slots per lane and piece the kernel is built for (see csrc/spmv_panel.cu)
-# a piece whose lanes finish on a common row (a row with more than `rounds` entries in the unit) takes the kernel's
-# slower segmented path: small pieces are chosen only while that stays rare
-MAX_SLOW_PIECES = 0.02
 FLAG_LONG_RUNS = 1          # FSB_PANEL_LONG_RUNS
+FLAG_RUNS = 2               # FSB_PANEL_RUNS
+# mean entries of a row inside one unit from which summing a run in a register beats one accumulator update per entry
+RUNS_MIN_MEAN = 1.5
 FLAG_DEBUG_TIMEOUT = 256    # FSB_PANEL_DEBUG_TIMEOUT
 MAX_ROW_NNZ = 512
 MIN_NNZ = 1 << 22
-NO_ROW = 0xFFFF
 
 
 class PanelLayout:
     """Device arrays of the regrouped matrix plus the launch geometry."""
 
     __slots__ = ("val", "rc", "unit_piece_ptr", "unit_chunk", "rb_unit_ptr", "n_row_blocks", "rb_rows", "chunk_cols",
-                 "n_buffers", "rounds", "flags", "max_run", "n_units", "n_pieces", "x_overhead", "slot_overhead",
-                 "status")
+                 "n_buffers", "rounds", "flags", "max_run", "pad_row", "n_units", "n_pieces", "x_overhead",
+                 "slot_overhead", "status")
 
     def nbytes(self):
         return sum(t.numel() * t.element_size() for t in (self.val, self.rc, self.unit_piece_ptr, self.unit_chunk,
@@ -148,11 +147,11 @@ def estimate_units(indices, indptr, n_rows, n_cols, rb_rows, chunk_cols):
     return None if scan is None else scan[0]
 
 
-def choose_rounds(nnz, long_runs):
-    """Smallest piece (rounds per lane) for which the pieces that need the kernel's segmented path stay rare."""
+def choose_rounds(long_runs):
+    """Smallest piece (rounds per lane) that holds every run of the matrix in one lane's rounds, so that the kernel
+    can add every product straight into its accumulator; the largest piece when some run is longer than that."""
     for k, rounds in enumerate(ROUNDS):
-        n_pieces = max(1.0, nnz / (32.0 * rounds))
-        if long_runs[k] <= MAX_SLOW_PIECES * n_pieces:
+        if long_runs[k] == 0:
             return rounds
     return ROUNDS[-1]
 
@@ -164,11 +163,12 @@ def _cumsum0(counts):
 
 
 def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, rounds, max_slot_overhead,
-                n_buffers=2):
+                n_buffers=2, pad_row=0xFFFF):
     """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of 32 * rounds
     slots and lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that
-    follow each other with the same key inside one unit form a run, which must not straddle two pieces.  Returns
-    (val, rc, first piece of each unit [n_units + 1], n_pieces, longest run), or None when a run does not fit in
+    follow each other with the same key inside one unit form a run, which must not straddle two pieces; pad_row:
+    the (spare) accumulator unused slots point at, with value 0 and column 0.  Returns
+    (val, rc, first piece of each unit [n_units + 1], n_pieces, longest run, number of runs), or None when a run does not fit in
     a piece or the padding exceeds max_slot_overhead."""
     dev = data_p.device
     nnz = data_p.numel()
@@ -227,10 +227,10 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     del pos_val
     word = (acc_p << 16) | field                         # fits 32 bits: accumulator index < 65535
     word = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
-    rc = torch.full((n_pieces * SLOTS,), NO_ROW << 16, dtype=torch.int64, device=dev)
+    rc = torch.full((n_pieces * SLOTS,), pad_row << 16, dtype=torch.int64, device=dev)
     rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
     rc[pos] = word
-    return val, rc, upiece, n_pieces, max_run
+    return val, rc, upiece, n_pieces, max_run, n_runs
 
 
 def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slot_overhead):
@@ -263,11 +263,11 @@ def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slo
     first_unit = torch.searchsorted(u_rb.contiguous(), torch.arange(b0, b0 + n_b, device=dev))
     u_ord = torch.arange(n_units, device=dev) - first_unit[u_rb - b0]
     packed = pack_pieces(data[e0:e1][perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord,
-                         CW, rounds, max_slot_overhead, n_buffers=NB)
+                         CW, rounds, max_slot_overhead, n_buffers=NB, pad_row=RB)
     if packed is None:
         return None
-    val, rc, upiece, n_pieces, max_run = packed
-    return val, rc, upiece, u_ch, u_rb, n_pieces, max_run
+    val, rc, upiece, n_pieces, max_run, n_runs = packed
+    return val, rc, upiece, u_ch, u_rb, n_pieces, max_run, n_runs
 
 
 def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False, rounds=None):
@@ -297,11 +297,11 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
             limit = MAX_X_OVERHEAD if sv == 4 else MAX_X_OVERHEAD_F64
             if not force and n_units * CW * sv > limit * nnz * (sv + 4):
                 return None
-            rounds = rounds or choose_rounds(nnz, long_runs)
+            rounds = rounds or choose_rounds(long_runs)
     SLOTS = 32 * rounds
     vals, rcs, upieces, chunks, blocks = [], [], [], [], []
     piece_base = 0
-    max_run = 0
+    max_run = n_runs = 0
     for r0, r1 in _slabs(indptr, n_rows, RB):
         part = _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB,
                            None if force else MAX_SLOT_OVERHEAD)
@@ -313,7 +313,8 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
             return None
         if part == ():
             continue                 # no entries in these rows
-        val_s, rc_s, upiece_s, u_ch_s, u_rb_s, n_pieces_s, max_run_s = part
+        val_s, rc_s, upiece_s, u_ch_s, u_rb_s, n_pieces_s, max_run_s, n_runs_s = part
+        n_runs += n_runs_s
         vals.append(val_s)
         rcs.append(rc_s)
         upieces.append(upiece_s[:-1] + piece_base)
@@ -340,8 +341,8 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     lay.unit_chunk = u_ch.to(torch.int32)
     lay.rb_unit_ptr = rb_unit_ptr.to(torch.int32)
     lay.n_row_blocks, lay.rb_rows, lay.chunk_cols, lay.n_buffers = n_rb, RB, CW, NB
-    lay.rounds, lay.max_run = rounds, max_run
-    lay.flags = FLAG_LONG_RUNS if max_run > rounds else 0
+    lay.rounds, lay.max_run, lay.pad_row = rounds, max_run, RB
+    lay.flags = (FLAG_LONG_RUNS if max_run > rounds else 0) | (FLAG_RUNS if nnz >= RUNS_MIN_MEAN * n_runs else 0)
     lay.n_units, lay.n_pieces = n_units, n_pieces
     lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
     lay.slot_overhead = n_pieces * SLOTS / float(nnz)

@@ -129,12 +129,15 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
  * 32 * rounds slots so that no row's entries straddle two pieces.
  *   val[s], rc[s]        per slot: value and packed word (local row << 16 | buffer * chunk_cols + local
  *                        column), buffer = ordinal of the unit inside its row block modulo n_buffers; unused
- *                        slots carry local row 0xFFFF
+ *                        slots carry value 0, column 0 and local row = rb_rows (a spare accumulator)
  *   rounds               4, 8 or 16: slots per lane and piece.  Small pieces suit units with few entries
  *                        (every warp of the CTA gets work in every unit)
- *   flags                FSB_PANEL_LONG_RUNS: some row has more than `rounds` entries inside one unit (never
- *                        more than a piece holds); the kernel then combines the lanes that finish on the same
- *                        row.  FSB_PANEL_DEBUG_TIMEOUT (tests only): the first copy of x of every CTA is made to
+ *   flags                FSB_PANEL_RUNS: rows have several entries per unit on average; the kernel then sums a
+ *                        row's products in a register and visits the accumulator once per run (otherwise once
+ *                        per entry, with no predicates).  Only speed depends on this flag.
+ *                        FSB_PANEL_LONG_RUNS: some row has more than `rounds` entries inside one unit (never
+ *                        more than a piece holds); the kernel then also combines the lanes that finish on the
+ *                        same row.  Must be set for such layouts.  FSB_PANEL_DEBUG_TIMEOUT (tests only): the first copy of x of every CTA is made to
  *                        look incomplete and the wait limit is lowered, so that the kernel takes its time-out
  *                        path -- it reports through `status` and returns without touching y
  *   n_buffers            2..8 chunks of x in shared memory (n_buffers * chunk_cols <= 65536): chunks are
@@ -148,9 +151,11 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
  * One CTA per row block keeps the block's y accumulators and n_buffers chunks of x in shared memory
  * (fsb_spmv_panel_smem_bytes() + fsb_spmv_panel_static_smem_bytes() must fit in 227 KiB; rb_rows < 65535).  Another stand-in for the launches of
  * _triton_spmv_csr_impl_opt_prepared (spmv_csr.py:329-376), for matrices whose rows span few column chunks.
- * status: optional device int32, set non-zero if a bounded wait on a bulk copy of x ran out.
+ * status: optional int32 in device memory or in page-locked host memory, set non-zero (a plain store) if a bounded
+ * wait on a bulk copy of x ran out.
  */
 #define FSB_PANEL_LONG_RUNS 1
+#define FSB_PANEL_RUNS 2
 #define FSB_PANEL_DEBUG_TIMEOUT 256
 int fsb_spmv_panel_piece_slots(int rounds);
 size_t fsb_spmv_panel_smem_bytes(int vtype, int rb_rows, int chunk_cols, int n_buffers);
@@ -168,7 +173,7 @@ int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc, const int
  * (spmv_csr.py:329-376 with the bucket tables :64-89: one Triton program per long row).
  * The picked rows are cut into groups; row q owns accumulators vbase[q] .. vbase[q+1]-1 ("virtual rows": at most
  * `rounds` entries of a virtual row in one column chunk) and the packed word of a slot holds the virtual row relative
- * to its group.  The units (group x column chunk) are ordered by group, then chunk, and dealt to n_ctas CTAs:
+ * to its group (unused slots: max_group_acc).  The units (group x column chunk) are ordered by group, then chunk, and dealt to n_ctas CTAs:
  *   cta_unit_ptr         units [cta_unit_ptr[c], cta_unit_ptr[c+1]) belong to CTA c (buffer of a slot's packed
  *                        word = ordinal of the unit inside its CTA modulo n_buffers)
  *   cta_group            group of CTA c;  group_cta_ptr: CTAs [group_cta_ptr[g], group_cta_ptr[g+1]) work on group g
@@ -220,7 +225,7 @@ int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, cons
  *   tile_row  from fsb_csr_tile_plan(tile_nnz = fsb_spmm_tile_nnz(vtype)).
  *   scratch   at least fsb_spmm_csr_scratch_bytes() bytes, 16-byte aligned (per-tile partial rows of
  *             rows that cross a tile boundary -- the counterpart of the reference's split workspace).
- *   status    optional DEVICE int32; set to a non-zero code if a bounded wait on a bulk copy ran out
+ *   status    optional int32 (device or page-locked host memory); set to a non-zero code if a bounded wait on a bulk copy ran out
  *             (the affected tiles are then left unwritten).  May be NULL.
  */
 size_t fsb_spmm_csr_scratch_bytes(int vtype, int64_t nnz, int64_t n_dense);

@@ -53,9 +53,9 @@ def _evaluate_long(lay, x):
                 a, field = w >> 16, w & 0xFFFF
                 for kk in range(16):   # race-freedom: the 32 slots of a round hold 32 different accumulators
                     ak = a[kk::16]
-                    ak = ak[ak != 0xFFFF]
+                    ak = ak[ak != lay.pad_row]
                     assert ak.size == np.unique(ak).size
-                live = a != 0xFFFF
+                live = a != lay.pad_row
                 assert live.any() and np.all(live[:live.sum()]) and np.all(vals[~live] == 0)
                 al, fl = a[live], field[live]
                 assert np.all(al < n_acc) and np.all(fl // CW == parity)

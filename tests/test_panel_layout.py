@@ -39,14 +39,19 @@ def _evaluate(lay, x, n_rows, n_cols, slots):
                 # the kernel's race-freedom: a lane adds to an accumulator where its row ends.  In every round but a
                 # lane's last one the lanes that do so are on different rows; in the last round two lanes may meet
                 # only in layouts flagged for the kernel's segmented path
-                nxt = np.append(rloc[1:], 0xFFFF)
-                nxt[R - 1::R] = 0xFFFF                      # a lane's run ends with its last slot
-                ends = (rloc != 0xFFFF) & (nxt != rloc)
+                nxt = np.append(rloc[1:], lay.pad_row)
+                nxt[R - 1::R] = lay.pad_row                      # a lane's run ends with its last slot
+                ends = (rloc != lay.pad_row) & (nxt != rloc)
                 for k in range(R):
                     rk = rloc[k::R][ends[k::R]]
                     if k < R - 1 or not (lay.flags & panel.FLAG_LONG_RUNS):
                         assert rk.size == np.unique(rk).size
-                live = rloc != 0xFFFF
+                    if not (lay.flags & panel.FLAG_LONG_RUNS):
+                        # the direct path adds every slot of a round: all its real rows must differ
+                        ak = rloc[k::R]
+                        ak = ak[ak != lay.pad_row]
+                        assert ak.size == np.unique(ak).size
+                live = rloc != lay.pad_row
                 assert live.any() and np.all(live[:live.sum()])            # real slots first, then padding
                 assert np.all(vals[~live] == 0)
                 rl, fl = rloc[live], field[live]
@@ -69,7 +74,10 @@ def test_layout_of_a_banded_matrix(fsb_lib, vdt, rounds):
     d, i, p = (torch.from_numpy(a) for a in S.generate_csr(spec, None, value_dtype=vdt))
     lay = panel.build_panel_layout(d, i, p, spec.n_rows, spec.n_cols, 70, force=True, rounds=rounds)
     assert lay is not None and lay.n_row_blocks * lay.rb_rows >= spec.n_rows
-    assert lay.rounds == (rounds or lay.rounds) and lay.rounds in panel.ROUNDS
+    assert lay.rounds == (rounds or lay.rounds) and lay.rounds in panel.ROUNDS and lay.pad_row == lay.rb_rows
+    if rounds is None:
+        assert lay.max_run <= lay.rounds and not (lay.flags & panel.FLAG_LONG_RUNS)  # no segmented path needed
+        assert lay.flags & panel.FLAG_RUNS                       # about two entries of a row per chunk here
     # rows of this matrix have up to a dozen entries in a chunk: small pieces must carry the long-run flag
     assert bool(lay.flags & panel.FLAG_LONG_RUNS) == (lay.max_run > lay.rounds)
     if rounds == 4:
@@ -133,11 +141,11 @@ def test_rows_with_long_runs(fsb_lib):
 
 
 def test_choice_of_piece_size():
-    # few long runs: the smallest piece; many: the next size whose share of slow pieces stays small
-    assert panel.choose_rounds(1 << 27, [100, 0, 0]) == 4
-    assert panel.choose_rounds(1 << 27, [1 << 22, 10, 0]) == 8
-    assert panel.choose_rounds(1 << 27, [1 << 22, 1 << 21, 5]) == 16
-    assert panel.choose_rounds(1 << 27, [1 << 22, 1 << 21, 1 << 20]) == 16
+    # the smallest piece whose rounds hold every run; the largest one when some run is longer than any
+    assert panel.choose_rounds([0, 0, 0]) == 4
+    assert panel.choose_rounds([100, 0, 0]) == 8
+    assert panel.choose_rounds([1 << 22, 10, 0]) == 16
+    assert panel.choose_rounds([1 << 22, 1 << 21, 5]) == 16
 
 
 def test_selection_rules(fsb_lib):
