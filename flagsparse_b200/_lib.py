@@ -16,6 +16,7 @@ FSB_I32, FSB_I64 = 0, 1
 FSB_SPMV_AUTO, FSB_SPMV_VECTOR, FSB_SPMV_STREAM = 0, 1, 2
 FSB_SPMV_PANEL = 3  # host-side tag only: the panel kernel has its own entry point
 FSB_SPMM_AUTO, FSB_SPMM_PLAIN, FSB_SPMM_BULK = 0, 1, 2
+FSB_SPMM_ACCUMULATE = 16  # or-ed into the selector: C += A B
 FSB_CUDA_ERROR_BASE = 1000
 
 _ERRORS = {

@@ -70,6 +70,14 @@ __device__ __forceinline__ void ld_dense(const V* p, V (&v)[VW]) {
   for (int i = 0; i < VW; ++i) v[i] = e[i];
 }
 template <typename V, int VW>
+__device__ __forceinline__ void ld_dense_stream(const V* p, V (&v)[VW]) {
+  typedef typename Vec<V, VW>::type VT;
+  VT t = __ldcs(reinterpret_cast<const VT*>(p));
+  const V* e = reinterpret_cast<const V*>(&t);
+#pragma unroll
+  for (int i = 0; i < VW; ++i) v[i] = e[i];
+}
+template <typename V, int VW>
 __device__ __forceinline__ void st_dense_stream(V* p, const V (&v)[VW]) {
   typedef typename Vec<V, VW>::type VT;
   VT t;

@@ -56,7 +56,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t phase)
   return false;
 }
 
-template <typename V, typename I, typename P, int VW, bool BULK>
+// ACCUM: add to what C holds instead of overwriting it (rows without entries are then left alone) -- the later
+// passes of a product that the host code splits into column panels of A.
+template <typename V, typename I, typename P, int VW, bool BULK, bool ACCUM>
 __global__ void __launch_bounds__(kMmThreads)
 spmm_tile_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P* __restrict__ ptr,
                  const V* __restrict__ B, int64_t ldb, V* __restrict__ C, int64_t ldc,
@@ -169,8 +171,15 @@ spmm_tile_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P*
         } else if (g == 0 && s_head_partial) {
 #pragma unroll
           for (int i = 0; i < VW; ++i) head[t * n_dense + col0 + i] = acc[i];
-        } else {
+        } else if (!ACCUM) {
           st_dense_stream<V, VW>(C + ((int64_t)ra + g) * ldc + col0, acc);
+        } else if (e > s) {
+          V* dst = C + ((int64_t)ra + g) * ldc + col0;
+          V old[VW];
+          ld_dense_stream<V, VW>(dst, old);
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[i] += old[i];
+          st_dense_stream<V, VW>(dst, acc);
         }
       }
     }
@@ -178,7 +187,7 @@ spmm_tile_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P*
 }
 
 // one thread per (tile t >= 1, column): finish the row that started before tile t and ends in it
-template <typename V, typename P>
+template <typename V, typename P, bool ACCUM>
 __global__ void __launch_bounds__(kMmThreads)
 spmm_fixup_kernel(const P* __restrict__ ptr, const int32_t* __restrict__ tile_row,
                   const V* __restrict__ carry, const V* __restrict__ head, V* __restrict__ C, int64_t ldc,
@@ -200,7 +209,8 @@ spmm_fixup_kernel(const P* __restrict__ ptr, const int32_t* __restrict__ tile_ro
     comp += (fabs(sum) >= fabs(v)) ? ((sum - s2) + v) : ((v - s2) + sum);
     sum = s2;
   }
-  C[(int64_t)ra * ldc + j] = (V)(sum + comp);
+  V* dst = C + (int64_t)ra * ldc + j;
+  *dst = ACCUM ? (V)(((double)*dst + sum) + comp) : (V)(sum + comp);
 }
 
 template <typename V>
@@ -218,6 +228,7 @@ struct SpmmArgs {
   void* C;
   int64_t ldc, n_rows, n_dense, nnz;
   int algo;
+  bool accumulate;
   const int32_t* tile_row;
   void* scratch;
   int32_t* status;
@@ -237,14 +248,16 @@ static int launch_spmm(const SpmmArgs& a) {
   V* head = carry + n_tiles * n_dense;
   bool bulk = a.algo != FSB_SPMM_PLAIN && aligned_to(a.data, 16) && aligned_to(a.idx, 16);
   dim3 grid((unsigned)n_tiles, (unsigned)col_tiles);
-  if (bulk)
-    spmm_tile_kernel<V, I, P, VW, true><<<grid, kMmThreads, 0, a.st>>>(
-        (const V*)a.data, (const I*)a.idx, (const P*)a.ptr, (const V*)a.B, a.ldb, (V*)a.C, a.ldc, a.tile_row,
-        carry, head, a.nnz, n_dense, LR, a.status);
-  else
-    spmm_tile_kernel<V, I, P, VW, false><<<grid, kMmThreads, 0, a.st>>>(
-        (const V*)a.data, (const I*)a.idx, (const P*)a.ptr, (const V*)a.B, a.ldb, (V*)a.C, a.ldc, a.tile_row,
-        carry, head, a.nnz, n_dense, LR, a.status);
+#define FSB_SPMM_LAUNCH(BULK_, ACC_)                                                                          \
+  spmm_tile_kernel<V, I, P, VW, BULK_, ACC_><<<grid, kMmThreads, 0, a.st>>>(                                  \
+      (const V*)a.data, (const I*)a.idx, (const P*)a.ptr, (const V*)a.B, a.ldb, (V*)a.C, a.ldc, a.tile_row,   \
+      carry, head, a.nnz, n_dense, LR, a.status)
+  if (bulk) {
+    if (a.accumulate) FSB_SPMM_LAUNCH(true, true); else FSB_SPMM_LAUNCH(true, false);
+  } else {
+    if (a.accumulate) FSB_SPMM_LAUNCH(false, true); else FSB_SPMM_LAUNCH(false, false);
+  }
+#undef FSB_SPMM_LAUNCH
   FSB_RETURN_IF_LAUNCH_FAILED();
   if (n_tiles > 1) {
     int log2_tile = 0;
@@ -252,8 +265,12 @@ static int launch_spmm(const SpmmArgs& a) {
     const int64_t n = (n_tiles - 1) * n_dense;
     const int64_t g = (n + kMmThreads - 1) / kMmThreads;
     if (g >= INT32_MAX) return FSB_ERANGE;
-    spmm_fixup_kernel<V, P><<<(unsigned)g, kMmThreads, 0, a.st>>>((const P*)a.ptr, a.tile_row, carry, head,
-                                                                 (V*)a.C, a.ldc, n_tiles, n_dense, log2_tile);
+    if (a.accumulate)
+      spmm_fixup_kernel<V, P, true><<<(unsigned)g, kMmThreads, 0, a.st>>>((const P*)a.ptr, a.tile_row, carry, head,
+                                                                         (V*)a.C, a.ldc, n_tiles, n_dense, log2_tile);
+    else
+      spmm_fixup_kernel<V, P, false><<<(unsigned)g, kMmThreads, 0, a.st>>>((const P*)a.ptr, a.tile_row, carry, head,
+                                                                          (V*)a.C, a.ldc, n_tiles, n_dense, log2_tile);
     FSB_RETURN_IF_LAUNCH_FAILED();
   }
   return FSB_OK;
@@ -300,6 +317,8 @@ extern "C" int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, c
   if ((vtype != FSB_F32 && vtype != FSB_F64) || (itype != FSB_I32 && itype != FSB_I64) ||
       (ptype != FSB_I32 && ptype != FSB_I64))
     return FSB_EINVAL;
+  const bool accumulate = (algo & FSB_SPMM_ACCUMULATE) != 0;
+  algo &= ~FSB_SPMM_ACCUMULATE;
   if (algo != FSB_SPMM_AUTO && algo != FSB_SPMM_PLAIN && algo != FSB_SPMM_BULK) return FSB_EINVAL;
   if (n_rows < 0 || n_cols < 0 || n_dense < 0 || nnz < 0) return FSB_EINVAL;
   if (n_rows >= INT32_MAX || n_cols >= INT32_MAX || n_dense >= (1 << 24)) return FSB_ERANGE;
@@ -308,6 +327,7 @@ extern "C" int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, c
   if (C == nullptr || indptr == nullptr || ldc < n_dense) return FSB_EINVAL;
   const size_t sv = vtype == FSB_F32 ? 4 : 8, si = itype == FSB_I32 ? 4 : 8, sp = ptype == FSB_I32 ? 4 : 8;
   if (!aligned_to(C, sv) || !aligned_to(indptr, sp)) return FSB_EALIGN;
+  if (nnz == 0 && accumulate) return FSB_OK;   // nothing to add
   if (nnz == 0) {
     const int64_t n = n_rows * n_dense;
     const int64_t g = (n + kMmThreads - 1) / kMmThreads;
@@ -326,7 +346,8 @@ extern "C" int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, c
   if (!aligned_to(scratch, 16)) return FSB_EALIGN;
   if (fsb_csr_num_tiles(nnz, kMmTile) >= 65535LL * 32768LL) return FSB_ERANGE;
 
-  SpmmArgs a{data, indices, indptr, B, ldb, C, ldc, n_rows, n_dense, nnz, algo, tile_row, scratch, status, st};
+  SpmmArgs a{data, indices, indptr, B, ldb, C, ldc, n_rows, n_dense, nnz, algo, accumulate, tile_row, scratch,
+             status, st};
 #define FSB_CASE(VT, V, IT, I, PT, P) \
   if (vtype == VT && itype == IT && ptype == PT) return spmm_typed<V, I, P>(a);
   FSB_CASE(FSB_F32, float, FSB_I32, int32_t, FSB_I32, int32_t)

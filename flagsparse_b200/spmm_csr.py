@@ -29,6 +29,59 @@ from ._common import (
 
 _SPMM_ALGO_NAMES = {"auto": _lib.FSB_SPMM_AUTO, "plain": _lib.FSB_SPMM_PLAIN, "bulk": _lib.FSB_SPMM_BULK}
 
+# A product whose gathers range over more of B than stays in L2 can be split: A into column panels (each panel's
+# slice of B at most this many bytes per column tile, so that it is fetched from DRAM about once) and B / C into
+# column tiles of one 128-byte line per row; passes after the first add to C.  Off by default (0): on the 2^20-row
+# matrix with 16 uniform entries per row every split measured slower than the single pass (width 32: 0.31 ms with
+# two panels, 0.43 ms with four, against 0.23 ms) -- a pass over rows of a few entries each is bound by the latency
+# of its read-add-write of C, not by the bytes it saves.  FSB_SPMM_PANEL_MB=<MiB> or FSB_SPMM_PANELS=<n> turn it on.
+PANEL_BYTES = 0
+COL_TILE_BYTES = 128
+SPAN_WINDOW = 1 << 20        # consecutive entries over which the column span is sampled
+
+
+def _panel_bytes():
+    v = os.environ.get("FSB_SPMM_PANEL_MB")
+    return PANEL_BYTES if v is None else int(float(v) * (1 << 20))
+
+
+class _CsrPart:
+    """CSR arrays of one column panel of A (or of all of A) plus the tile plan and scratch the kernel needs."""
+
+    __slots__ = ("data", "kernel_indices", "kernel_indptr", "n_rows", "tile_row", "_scratch")
+
+    def __init__(self, data, kernel_indices, kernel_indptr, n_rows, tile_nnz):
+        self.data, self.kernel_indices, self.kernel_indptr, self.n_rows = data, kernel_indices, kernel_indptr, n_rows
+        self.tile_row = _tile_plan(kernel_indptr, n_rows, data.numel(), tile_nnz) if data.numel() > 0 and n_rows > 0 \
+            else None
+        self._scratch = {}
+
+    def scratch_for(self, n_dense):
+        buf = self._scratch.get(n_dense)
+        if buf is None:
+            nbytes = int(_lib.lib().fsb_spmm_csr_scratch_bytes(_VTYPE[self.data.dtype], self.data.numel(), n_dense))
+            buf = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.data.device)
+            self._scratch = {n_dense: buf}  # keep one width at a time
+        return buf
+
+
+def split_by_column_panels(data, indices, indptr, n_rows, n_cols, n_panels):
+    """CSR arrays (data, indices, indptr) of the n_panels column panels of A: panel p holds the entries whose
+    column lies in [p * w, (p + 1) * w), w = ceil(n_cols / n_panels), in their original order; every panel keeps
+    all n_rows rows (rows without entries in a panel are empty there)."""
+    w = -(-n_cols // n_panels)
+    lens = (indptr[1:] - indptr[:-1]).to(torch.int64)
+    rows = torch.repeat_interleave(torch.arange(n_rows, device=data.device), lens)
+    panel_of = torch.div(indices.to(torch.int64), w, rounding_mode="floor")
+    out = []
+    for p in range(n_panels):
+        keep = panel_of == p
+        counts = torch.bincount(rows[keep], minlength=n_rows)
+        ptr = torch.zeros(n_rows + 1, dtype=indptr.dtype, device=data.device)
+        ptr[1:] = torch.cumsum(counts, 0).to(indptr.dtype)
+        out.append((data[keep].contiguous(), indices[keep].contiguous(), ptr))
+    return out
+
 
 def _prepare_spmm_csr_matrix(data, indices, indptr, shape):
     """Checks of the reference's function of this name (spmm_csr.py:197-255), in its order.  Returns
@@ -85,6 +138,15 @@ def _check_spmm_dense(B, data, n_cols):
         raise ValueError("B must be on the same CUDA device as the sparse matrix")
     if B.dtype != data.dtype:
         raise TypeError("B dtype must match data dtype")
+    return _row_major(B)
+
+
+def _row_major(B):
+    """B as the kernel can read it: unit stride along a row, any stride between rows (the reference copies every
+    non-contiguous B, spmm_csr.py:280; a row-strided view needs no copy here)."""
+    if B.shape[1] <= 1 or B.stride(1) == 1:
+        if B.shape[0] <= 1 or B.stride(0) >= B.shape[1]:
+            return B
     return B.contiguous()
 
 
@@ -155,7 +217,7 @@ class PreparedCsrSpmmOpt:
         "data", "kernel_indices", "kernel_indptr", "shape", "n_rows", "n_cols", "max_row_nnz",
         "row_buckets", "supports_opt", "long_part_rows", "long_part_starts", "long_part_ends",
         "long_row_ids", "long_row_part_ptr", "long_row_fallback_only", "stats", "tile_nnz", "tile_row",
-        "_scratch", "_status", "_row_lengths", "wide",
+        "_scratch", "_status", "_row_lengths", "wide", "_whole", "_panels", "_span",
     )
 
     def __init__(self, data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, tile_nnz, tile_row,
@@ -173,6 +235,7 @@ class PreparedCsrSpmmOpt:
         self.tile_row = tile_row
         n_tiles = 0 if tile_row is None else tile_row.numel() - 1
         self.row_buckets = [{"kind": "tiles", "tile_nnz": tile_nnz, "n_tiles": n_tiles, "n_rows": self.n_rows}]
+        self._scratch = None
         self.supports_opt = data.dtype in (torch.float32, torch.float64)
         self.long_part_rows = torch.empty((0,), dtype=torch.int32, device=dev)
         self.long_part_starts = torch.empty((0,), dtype=torch.int64, device=dev)
@@ -180,9 +243,11 @@ class PreparedCsrSpmmOpt:
         self.long_row_ids = torch.empty((0,), dtype=torch.int32, device=dev)
         self.long_row_part_ptr = torch.zeros(1, dtype=torch.int64, device=dev)
         self.long_row_fallback_only = False
-        self._scratch = {}
         self._status = None
         self._row_lengths = None
+        self._whole = None       # the matrix as one _CsrPart (shares the tile plan)
+        self._panels = {}        # number of column panels -> list of _CsrPart
+        self._span = None        # columns spanned by a window of consecutive entries (median over samples)
         # float16 / bfloat16 / complex values: (kind, prepared real matrices) the products go through (widetypes.py)
         self.wide = wide
 
@@ -193,13 +258,74 @@ class PreparedCsrSpmmOpt:
             self._row_lengths = p[1:] - p[:-1] if self.n_rows > 0 else p.new_empty((0,))
         return self._row_lengths
 
-    def scratch_for(self, n_dense):
-        buf = self._scratch.get(n_dense)
-        if buf is None:
-            nbytes = int(_lib.lib().fsb_spmm_csr_scratch_bytes(_VTYPE[self.data.dtype], self.data.numel(), n_dense))
-            buf = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.data.device)
-            self._scratch = {n_dense: buf}  # keep one width at a time
-        return buf
+    # -- how a product of a given width is run --------------------------------------------------------------
+    def column_span(self):
+        """Median number of columns between the smallest and the largest column index inside windows of
+        SPAN_WINDOW consecutive entries: about how many rows of B the CTAs running at one time gather from."""
+        if self._span is None:
+            idx = self.kernel_indices
+            nnz = idx.numel()
+            if nnz == 0:
+                self._span = 0
+            else:
+                k = max(1, min(64, nnz // SPAN_WINDOW))
+                win = min(SPAN_WINDOW, nnz)
+                starts = [(nnz - win) * j // max(1, k - 1) if k > 1 else 0 for j in range(k)]
+                spans = [int(idx[s0:s0 + win].max()) - int(idx[s0:s0 + win].min()) + 1 for s0 in starts[:8]]
+                spans.sort()
+                self._span = spans[len(spans) // 2]
+        return self._span
+
+    def n_panels_for(self, n_dense):
+        """Column panels of A for a product of this width (1 = the matrix as it is)."""
+        forced = int(os.environ.get("FSB_SPMM_PANELS", "0"))
+        if forced > 0:
+            return forced
+        limit = _panel_bytes()
+        if limit <= 0 or self.tile_row is None:
+            return 1
+        sv = self.data.element_size()
+        row_bytes = min(n_dense * sv, COL_TILE_BYTES)
+        if self.column_span() * row_bytes <= limit:
+            return 1                                  # the gathers of concurrent CTAs stay within what L2 holds
+        return max(1, min(16, -(-self.n_cols * row_bytes // limit)))
+
+    def parts_for(self, n_panels):
+        if n_panels == 1:
+            if self._whole is None:
+                part = _CsrPart.__new__(_CsrPart)
+                part.data, part.kernel_indices, part.kernel_indptr = self.data, self.kernel_indices, self.kernel_indptr
+                part.n_rows, part.tile_row, part._scratch = self.n_rows, self.tile_row, {}
+                self._whole = part
+            return [self._whole]
+        parts = self._panels.get(n_panels)
+        if parts is None:
+            triples = split_by_column_panels(self.data, self.kernel_indices, self.kernel_indptr, self.n_rows,
+                                             self.n_cols, n_panels)
+            parts = [_CsrPart(d, i, p, self.n_rows, self.tile_nnz) for d, i, p in triples]
+            self._panels = {n_panels: parts}          # keep one split at a time
+        return parts
+
+    def passes_for(self, n_dense):
+        """[(part, first column, width, accumulate)]: the launches of one product, in order."""
+        n_panels = self.n_panels_for(n_dense)
+        parts = self.parts_for(n_panels)
+        sv = self.data.element_size()
+        tile = n_dense if n_panels == 1 else max(1, COL_TILE_BYTES // sv)
+        out = []
+        for c0 in range(0, n_dense, tile):
+            for k, part in enumerate(parts):
+                out.append((part, c0, min(tile, n_dense - c0), k > 0))
+        return out
+
+    def launches_per_product(self, n_dense):
+        return sum(2 if (part.tile_row is not None and part.tile_row.numel() > 2) else 1
+                   for part, _, _, _ in self.passes_for(n_dense))
+
+    def plan_summary(self, n_dense):
+        passes = self.passes_for(n_dense)
+        return {"column_panels_of_A": self.n_panels_for(n_dense), "column_tiles_of_B": len({c for _, c, _, _ in passes}),
+                "passes": len(passes), "column_span": self.column_span(), "panel_bytes_limit": _panel_bytes()}
 
     def status_word(self):
         if self._status is None:
@@ -238,7 +364,8 @@ def prepare_spmm_csr_opt(data, indices, indptr, shape):
 
 def _spmm_launch(prepared, B, C):
     """Enqueue C = A B on the current stream.  Stands in for _triton_spmm_csr_impl (spmm_csr.py:525-599)
-    and _triton_spmm_csr_impl_opt_prepared (:1033-1055)."""
+    and _triton_spmm_csr_impl_opt_prepared (:1033-1055).  One launch of the tiled kernel per pass: the whole
+    product, or (column panel of A) x (column tile of B) passes when B is too large to be gathered from L2."""
     L = _lib.lib()
     p = prepared
     dev = p.data.device
@@ -246,19 +373,25 @@ def _spmm_launch(prepared, B, C):
     if p.n_rows == 0 or n_dense == 0:
         return
     algo = _SPMM_ALGO_NAMES.get(os.environ.get("FSB_SPMM_ALGO", "auto").strip().lower(), _lib.FSB_SPMM_AUTO)
-    scratch = p.scratch_for(n_dense) if p.tile_row is not None else None
-    p.status_word().poll()
+    status = p.status_word()
+    status.poll()
+    sv = B.element_size()
+    vt, it, pt = _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype]
+    ldb, ldc = B.stride(0), C.stride(0)
+    stream = _stream_ptr(dev)
     with torch.cuda.device(dev):
-        rc = L.fsb_spmm_csr(
-            _VTYPE[p.data.dtype], _ITYPE[p.kernel_indices.dtype], _ITYPE[p.kernel_indptr.dtype],
-            _ptr(p.data), _ptr(p.kernel_indices), p.kernel_indptr.data_ptr(), _ptr(B), B.stride(0),
-            C.data_ptr(), C.stride(0), p.n_rows, p.n_cols, n_dense, p.data.numel(), algo,
-            None if p.tile_row is None else p.tile_row.data_ptr(),
-            None if scratch is None else scratch.data_ptr(), 0 if scratch is None else scratch.numel(),
-            p.status_word().data_ptr(), _stream_ptr(dev),
-        )
-    _lib.check(rc, "fsb_spmm_csr")
-    p.status_word().posted("fsb_spmm_csr")
+        for part, c0, width, accumulate in p.passes_for(n_dense):
+            scratch = part.scratch_for(width) if part.tile_row is not None else None
+            rc = L.fsb_spmm_csr(
+                vt, it, pt, _ptr(part.data), _ptr(part.kernel_indices), part.kernel_indptr.data_ptr(),
+                B.data_ptr() + c0 * sv, ldb, C.data_ptr() + c0 * sv, ldc, p.n_rows, p.n_cols, width,
+                part.data.numel(), algo | (_lib.FSB_SPMM_ACCUMULATE if accumulate else 0),
+                None if part.tile_row is None else part.tile_row.data_ptr(),
+                None if scratch is None else scratch.data_ptr(), 0 if scratch is None else scratch.numel(),
+                status.data_ptr(), stream,
+            )
+            _lib.check(rc, "fsb_spmm_csr")
+    status.posted("fsb_spmm_csr")
 
 
 def _check_out(out, device, shape, dtype, device_msg):
@@ -367,4 +500,4 @@ def flagsparse_spmm_csr_opt(data=None, indices=None, indptr=None, B=None, shape=
         raise ValueError(f"B.shape[0] must be n_cols={prepared.n_cols}, got {B.shape[0]}")
     if B.ndim != 2:
         raise ValueError("B must be a 2D dense tensor")
-    return _run_spmm(prepared, B.contiguous(), out, return_time)
+    return _run_spmm(prepared, _row_major(B), out, return_time)

@@ -54,6 +54,7 @@ extern "C" {
 #define FSB_SPMM_AUTO 0
 #define FSB_SPMM_PLAIN 1     /* tile of data/indices staged in shared memory by ordinary loads   */
 #define FSB_SPMM_BULK 2      /* tile staged by cp.async.bulk (TMA 1-D bulk copy) + mbarrier       */
+#define FSB_SPMM_ACCUMULATE 16 /* or-ed into the selector: C += A B instead of C = A B            */
 
 int fsb_version(void);
 
@@ -222,6 +223,11 @@ int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, cons
  * C is n_rows x n_dense with leading dimension ldc.  Replaces _triton_spmm_csr_impl
  * (spmm_csr.py:525-599, kernel :92-134) and _triton_spmm_csr_impl_opt_prepared (:1033-1055, kernels
  * :602-919, split workspace :976-1030).  Every C[i, j] is written exactly once per call.
+ *   algo      staging selector, optionally or-ed with FSB_SPMM_ACCUMULATE: the product is then added to what C
+ *             holds (rows of A without entries leave their row of C untouched).  The host code uses it to
+ *             multiply by column panels of A one after the other, each panel's slice of B small enough to stay
+ *             in L2 while it is gathered from, and by column tiles of B / C (pass the tile's first element and the
+ *             full leading dimensions).
  *   tile_row  from fsb_csr_tile_plan(tile_nnz = fsb_spmm_tile_nnz(vtype)).
  *   scratch   at least fsb_spmm_csr_scratch_bytes() bytes, 16-byte aligned (per-tile partial rows of
  *             rows that cross a tile boundary -- the counterpart of the reference's split workspace).

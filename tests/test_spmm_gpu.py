@@ -83,6 +83,46 @@ def test_noncontiguous_b_out_and_determinism(cuda, fsb_lib):
     assert torch.equal(wide[:, ::2], c) and c5.data_ptr() == wide.data_ptr()
 
 
+@pytest.mark.parametrize("vdt", ["float32", "float64"])
+@pytest.mark.parametrize("n_panels", [2, 3])
+def test_column_panels_and_tiles(cuda, fsb_lib, vdt, n_panels):
+    """The split product (column panels of A, column tiles of B and C, later passes adding to C) on a matrix with
+    long rows that cross tile boundaries, empty rows, a width that is not a multiple of the tile, a row-strided B
+    and a row-strided C."""
+    lens = ([0, 3, 40, 0, 1, 2500, 7, 0] * 60) + [9000, 0, 0, 5]
+    data, idx, ptr = handmade_csr(21, lens, 3000, value_dtype=np.dtype(vdt).type, sort=False, replace=True)
+    n_rows, n_dense = len(lens), 72
+    rng = np.random.default_rng(5)
+    b_wide = rng.uniform(-1, 1, (3000, 100)).astype(vdt)
+    bd = dev(b_wide)[:, 10:10 + n_dense]                       # rows 100 elements apart
+    assert not bd.is_contiguous()
+    with env(FSB_SPMM_PANELS=n_panels):
+        prep = fs.prepare_spmm_csr_opt(dev(data), dev(idx), dev(ptr), (n_rows, 3000))
+        passes = prep.passes_for(n_dense)
+        tile = 128 // np.dtype(vdt).itemsize
+        assert len(passes) == n_panels * -(-n_dense // tile) and prep.launches_per_product(n_dense) >= len(passes)
+        c = fs.flagsparse_spmm_csr_opt(B=bd, prepared=prep)
+        assert_spmm_ok(c.cpu().numpy(), data, idx, ptr, (n_rows, 3000), b_wide[:, 10:10 + n_dense])
+        assert np.all(c.cpu().numpy()[np.asarray(lens) == 0] == 0)
+        assert torch.equal(fs.flagsparse_spmm_csr_opt(B=bd, prepared=prep), c)     # bit-reproducible
+        out_wide = torch.full((n_rows, 96), 7.0, dtype=bd.dtype, device="cuda:0")
+        view = out_wide[:, 8:8 + n_dense]
+        c2 = fs.flagsparse_spmm_csr_opt(B=bd, prepared=prep, out=view)
+        assert torch.equal(view, c) and c2.data_ptr() == view.data_ptr()
+        assert torch.all(out_wide[:, :8] == 7.0) and torch.all(out_wide[:, 8 + n_dense:] == 7.0)
+        with env(FSB_SPMM_ALGO="plain"):
+            assert torch.equal(fs.flagsparse_spmm_csr_opt(B=bd, prepared=prep), c)
+        prep.check_status()
+    # one-shot entry point and goldens through the split path
+    with env(FSB_SPMM_PANELS=n_panels):
+        for path in golden_files("spmm"):
+            g = load_golden(path)
+            if g["data"].dtype != np.dtype(vdt):
+                continue
+            cg = spmm(g["data"], g["indices"], g["indptr"], g["shape"], g["B"])
+            assert_spmm_ok(cg, g["data"], g["indices"], g["indptr"], g["shape"], g["B"], what=path)
+
+
 @pytest.mark.parametrize("n_dense", [32, 64, 128])
 def test_config_c4_full_size(cuda, fsb_lib, n_dense):
     spec = S.config_spec("c4")
@@ -90,6 +130,11 @@ def test_config_c4_full_size(cuda, fsb_lib, n_dense):
     b = S.dense_vector(spec, spec.n_cols, "cuda:0", n_dense=n_dense)
     prep = fs.prepare_spmm_csr_opt(d, i, p, (spec.n_rows, spec.n_cols))
     c = fs.flagsparse_spmm_csr_opt(B=b, prepared=prep)
+    assert prep.n_panels_for(n_dense) == 1          # one pass by default
+    with env(FSB_SPMM_PANEL_MB=64):                 # B gathered panel by panel (64 MiB per pass and column tile)
+        assert prep.n_panels_for(n_dense) == 2
+        split = fs.flagsparse_spmm_csr_opt(B=b, prepared=prep)
+    check_spmm_blocks(spec, split, b.cpu().numpy(), sample_blocks(spec.n_rows, 4, 1024, seed=3))
     worst = check_spmm_blocks(spec, c, b.cpu().numpy(), sample_blocks(spec.n_rows, 12, 1024))
     assert torch.equal(fs.flagsparse_spmm_csr_opt(B=b * 2, prepared=prep), c * 2)  # exact under power-of-two scaling
     with env(FSB_SPMM_ALGO="plain"):
