@@ -8,6 +8,7 @@ row-major B.  Compute goes through libfsb.so (include/fsb.h); there is no Triton
 from ._common import SUPPORTED_INDEX_DTYPES, SUPPORTED_VALUE_DTYPES, _tolerance_for_dtype
 from .coo import PreparedCoo, flagsparse_spmm_coo, flagsparse_spmv_coo, prepare_spmv_coo
 from .mtx import load_mtx_to_csr_torch
+from .sddmm_csr import SDDMMPrepared, flagsparse_sddmm_csr, prepare_sddmm_csr
 from .sharded import ShardedCsrSpmm, ShardedCsrSpmv, partition_rows_by_nnz
 from .spmm_csr import (
     PreparedCsrSpmmOpt,
@@ -41,6 +42,9 @@ __all__ = [
     "prepare_spmm_csr_opt",
     "flagsparse_spmm_csr",
     "flagsparse_spmm_csr_opt",
+    "SDDMMPrepared",
+    "prepare_sddmm_csr",
+    "flagsparse_sddmm_csr",
     "load_mtx_to_csr_torch",
     "ShardedCsrSpmv",
     "ShardedCsrSpmm",

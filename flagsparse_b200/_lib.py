@@ -57,6 +57,8 @@ SIGNATURES = {
         _i32,
         [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp, _vp],
     ),
+    "fsb_sddmm_csr": (_i32, [_i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double,
+                             _c.c_double, _vp]),
 }
 
 _lib = None

@@ -240,6 +240,18 @@ int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, const void* 
                  int64_t n_cols, int64_t n_dense, int64_t nnz, int algo, const int32_t* tile_row,
                  void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
 
+/*
+ * Sampled dense-dense product on a CSR pattern: out[p] = alpha * dot(X[row(p), :], Y[indices[p], :]) + beta * data[p]
+ * for every entry p.  X is n_rows x k_dim and Y is n_cols x k_dim, row-major with leading dimensions ldx / ldy
+ * (elements); row_ids[p] is the row of entry p (int32, built once per pattern from indptr); data may be NULL (then
+ * beta is ignored); out has nnz elements and may alias data.  Dot products are accumulated in the value type.
+ * Replaces the launch in _run_sddmm_prepared (src/flagsparse/sparse_operations/sddmm_csr.py:265-347, kernel
+ * :107-152); the row-id array is the reference's too (:83-91).
+ */
+int fsb_sddmm_csr(int vtype, const int32_t* indices, const int32_t* row_ids, const void* X, int64_t ldx,
+                  const void* Y, int64_t ldy, const void* data, void* out, int64_t n_rows, int64_t n_cols,
+                  int64_t nnz, int64_t k_dim, double alpha, double beta, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -77,6 +77,23 @@ def spmv_rowloop(data, indices, indptr, shape, x, acc_dtype=None):
     return y
 
 
+def sddmm_f64(data, indices, indptr, x, y, alpha=1.0, beta=0.0):
+    """(out_ref, magnitude) of out[p] = alpha * dot(x[row(p)], y[col(p)]) + beta * data[p] in float64, and
+    |alpha| * dot(|x[row]|, |y[col]|) + |beta| * |data[p]| -- the definition the reference's kernel implements
+    (src/flagsparse/sparse_operations/sddmm_csr.py:107-152) and checks itself against (:424-440)."""
+    indptr = np.asarray(indptr, dtype=np.int64)
+    rows = np.repeat(np.arange(indptr.shape[0] - 1), np.diff(indptr))
+    cols = np.asarray(indices, dtype=np.int64)
+    x64, y64 = np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64)
+    out = alpha * np.einsum("pk,pk->p", x64[rows], y64[cols])
+    mag = abs(alpha) * np.einsum("pk,pk->p", np.abs(x64[rows]), np.abs(y64[cols]))
+    if data is not None:
+        d64 = np.asarray(data, dtype=np.float64)
+        out = out + beta * d64
+        mag = mag + abs(beta) * np.abs(d64)
+    return out, mag
+
+
 def max_bound_ratio(got, ref, mag):
     """max_i |got_i - ref_i| / mag_i with 0/0 = 0: the quantity the acceptance bound limits by `tol`."""
     got = np.asarray(got, dtype=np.float64)

@@ -19,8 +19,11 @@ plus the pure host helpers (_resolve_spmm_alg1_launch_config, _select_spmm_opt_b
 coo_to_csr_for_spmv), and the Matrix Market loader of the reference's benchmark scripts
   load_mtx_to_csr_torch  (tests/test_spmv.py:29-103 and tests/test_spmm.py:163-268 of the reference)
 on the small files of tests/golden/mtx/, and the base SpMV / SpMM paths on float16, bfloat16, complex64 and
-complex128 values (the same two launch helpers; the reference widens or takes real views there).
-`--only coo` / `--only mtx` / `--only wide` regenerate those fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
+complex128 values (the same two launch helpers; the reference widens or takes real views there), and
+  SDDMM          _sddmm_csr_real_kernel launched as _run_sddmm_prepared launches it
+                 (src/flagsparse/sparse_operations/sddmm_csr.py:107-152, 265-347), on a pattern prepared by the
+                 same steps as prepare_sddmm_csr (:83-104) without its CUDA check.
+`--only coo` / `--only mtx` / `--only wide` / `--only sddmm` regenerate those fixtures alone.  Inputs and outputs are stored together, so the fixtures stay valid even if the
 synthetic generator changes.  Nothing here is imported by the package, the tests or the benchmark.
 """
 
@@ -232,6 +235,44 @@ def make_wide(index, R, M):
         print("wide", tag, index["wide"][tag], flush=True)
 
 
+def make_sddmm(index, D):
+    """Outputs of the reference's SDDMM kernel (value-dtype accumulation, its default variant)."""
+    import triton
+    import triton.language as tl
+
+    index["sddmm"] = {}
+    lens = [0, 3, 0, 17, 1, 64, 0, 0, 5, 140, 2, 0]
+    cases = {
+        "k8_f32": (handmade_csr(41, lens, 150, np.float32, np.int32, np.int32), 150, 8, 1.0, 0.0, False),
+        "k33_f32_beta": (handmade_csr(42, lens, 150, np.float32, np.int32, np.int64), 150, 33, 0.5, -2.0, True),
+        "k64_f32": (handmade_csr(43, [16] * 40, 97, np.float32, np.int32, np.int32), 97, 64, -1.25, 0.0, False),
+        "k130_f64_beta": (handmade_csr(44, lens, 150, np.float64, np.int32, np.int32), 150, 130, 2.0, 0.75, True),
+        "k4_f64": (handmade_csr(45, [7] * 30, 64, np.float64, np.int32, np.int64), 64, 4, 1.0, 0.0, False),
+    }
+    for name, ((data, indices, indptr), n_cols, k, alpha, beta, has_in) in cases.items():
+        n_rows = indptr.shape[0] - 1
+        rng = np.random.default_rng(sum(ord(ch) for ch in name))
+        x = rng.uniform(-1, 1, (n_rows, k)).astype(data.dtype)
+        y = rng.uniform(-1, 1, (n_cols, k)).astype(data.dtype)
+        t_idx, t_ptr = _t(indices), _t(indptr).to(torch.int64)
+        row_ids = D._build_row_ids(t_ptr)
+        tx, ty, td = _t(x), _t(y), _t(data)
+        nnz = int(t_idx.numel())
+        out = torch.empty(nnz, dtype=tx.dtype)
+        block_k, num_warps = D._resolve_sddmm_launch_config(k)
+        acc = tl.float64 if tx.dtype == torch.float64 else tl.float32
+        D._sddmm_csr_real_kernel[(triton.cdiv(nnz, 128),)](
+            t_idx, row_ids, tx, ty, td if has_in else out, out, nnz, k, tx.stride(0), tx.stride(1), ty.stride(0),
+            ty.stride(1), float(alpha), float(beta), HAS_IN=has_in, BLOCK_P=128, BLOCK_K=block_k, ACC_DTYPE=acc,
+            num_warps=num_warps)
+        np.savez_compressed(os.path.join(HERE, f"sddmm_{name}.npz"), data=data, indices=indices, indptr=indptr,
+                            shape=np.asarray((n_rows, n_cols)), x=x, y=y, alpha=np.float64(alpha),
+                            beta=np.float64(beta), has_in=np.asarray(has_in), out=out.numpy(),
+                            row_ids=row_ids.numpy())
+        index["sddmm"][name] = {"nnz": nnz, "k": k, "block_k": block_k, "num_warps": num_warps}
+        print("sddmm", name, nnz, k, flush=True)
+
+
 def make_mtx(index, reference_root):
     """CSR arrays the reference's two loaders produce for tests/golden/mtx/*.mtx (float32 and float64, on CPU)."""
     import glob
@@ -283,22 +324,25 @@ def host_helper_goldens(R, M):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference project")
-    ap.add_argument("--only", choices=("all", "coo", "mtx", "wide"), default="all")
+    ap.add_argument("--only", choices=("all", "coo", "mtx", "wide", "sddmm"), default="all")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from flagsparse.sparse_operations import spmm_coo as MC  # noqa: E402
     from flagsparse.sparse_operations import spmm_csr as M  # noqa: E402
     from flagsparse.sparse_operations import spmv_coo as V  # noqa: E402
     from flagsparse.sparse_operations import spmv_csr as R  # noqa: E402
+    from flagsparse.sparse_operations import sddmm_csr as D  # noqa: E402
 
     index_path = os.path.join(HERE, "index.json")
-    if args.only in ("coo", "mtx", "wide"):
+    if args.only in ("coo", "mtx", "wide", "sddmm"):
         with open(index_path) as f:
             index = json.load(f)
         if args.only == "coo":
             make_coo(index, V, MC)
         elif args.only == "wide":
             make_wide(index, R, M)
+        elif args.only == "sddmm":
+            make_sddmm(index, D)
         else:
             make_mtx(index, args.reference)
         with open(index_path, "w") as f:
@@ -320,6 +364,7 @@ def main():
     make_coo(index, V, MC)
     make_mtx(index, args.reference)
     make_wide(index, R, M)
+    make_sddmm(index, D)
     index["host"] = host_helper_goldens(R, M)
     with open(index_path, "w") as f:
         json.dump(index, f, indent=1, sort_keys=True)
