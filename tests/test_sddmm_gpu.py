@@ -97,7 +97,6 @@ def test_edge_shapes_and_strides(cuda, fsb_lib):
         yw = rng.uniform(-1, 1, (n_cols, 44)).astype(np.float32)
         for lo, k in ((0, 40), (0, 36), (1, 33), (4, 32), (3, 1)):
             xd, yd = dev(xw)[:, lo:lo + k], dev(yw)[:, lo:lo + k]
-            assert not xd.is_contiguous() or k == 40
             out = fs.flagsparse_sddmm_csr(dev(data), dev(indices), dev(indptr), xd, yd, (len(lens), n_cols), beta=1.0)
             _check(out, data, indices, indptr, xw[:, lo:lo + k], yw[:, lo:lo + k], 1.0, 1.0, f"{lens[:3]} {lo}:{k}")
     # column-major operands are copied by the entry point, as the reference's .contiguous() does
