@@ -21,7 +21,21 @@ import flagsparse_b200 as fs
 from flagsparse_b200 import synthetic as S
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-PEAK_GBS = 6547.5   # measured copy bandwidth of the B200s this was written on; only the last column depends on it
+
+
+def _peak_gbs():
+    """Measured copy bandwidth (GB/s) from MEASURED_PEAKS.json at the repository root; 6650 when the file is absent
+    (an earlier measurement on the same kind of GPU).  Only the last column of the table depends on it."""
+    import json
+
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError, TypeError):
+        return 6650.0
+
+
+PEAK_GBS = _peak_gbs()
 
 
 class Report:

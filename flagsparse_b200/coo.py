@@ -18,7 +18,7 @@ import time
 import torch
 
 from ._common import SUPPORTED_INDEX_DTYPES, _INDEX_LIMIT_INT32, _check_value_dtype
-from .spmm_csr import _check_out, _run_spmm, _select_spmm_alg1_warp_and_factor, prepare_spmm_csr_opt
+from .spmm_csr import _alg1_shape, _check_out, _run_spmm, prepare_spmm_csr_opt
 from .spmv_csr import _prepare_spmv_csr, _spmv_launch
 
 
@@ -85,16 +85,16 @@ def _row_pointer(row_sorted64, n_rows):
 
 def _prepare_coo_tensors(data, row, col, shape, sort_by_row, reuse_expected):
     if not all(torch.is_tensor(t) for t in (data, row, col)):
-        raise TypeError("data, row, col must all be torch.Tensor")
+        raise TypeError("data, row and col have to be torch.Tensor objects")
     if data.ndim != 1 or row.ndim != 1 or col.ndim != 1:
-        raise ValueError("data, row, col must be 1D")
+        raise ValueError("data, row and col have to be one-dimensional")
     if not all(t.is_cuda for t in (data, row, col)):
-        raise ValueError("data, row, col must be CUDA tensors")
+        raise ValueError("data, row and col have to live on a CUDA device")
     n_rows, n_cols = int(shape[0]), int(shape[1])
     if data.numel() != row.numel() or data.numel() != col.numel():
-        raise ValueError("data, row, col must have the same length")
+        raise ValueError(f"{data.numel()} values, {row.numel()} row ids, {col.numel()} column ids: the counts differ")
     if data.dtype not in (torch.float32, torch.float64):
-        raise TypeError("this COO SpMV path supports float32/float64 only (use CSR for other dtypes)")
+        raise TypeError(f"COO SpMV takes float32 or float64 values, not {data.dtype} (the CSR entry points take more)")
     row64 = row.to(torch.int64)
     col64 = col.to(torch.int64)
     _check_index_range(row64, col64, n_rows, n_cols)
@@ -125,19 +125,11 @@ def prepare_spmv_coo(data, row, col, shape, sort_by_row=True):
 
 
 def _validate_x_coo(x, prepared):
-    if x is None or not torch.is_tensor(x):
-        raise TypeError("x must be a torch.Tensor")
-    if x.ndim != 1:
-        raise ValueError("x must be a 1D tensor")
-    if not x.is_cuda:
-        raise ValueError("x must be a CUDA tensor")
-    if x.dtype != prepared.data.dtype:
-        raise TypeError("x dtype must match sparse matrix dtype")
-    if x.numel() != prepared.n_cols:
-        raise ValueError(f"x length must be n_cols={prepared.n_cols}, got {x.numel()}")
-    if x.device != prepared.data.device:
-        raise ValueError("x must be on the same device as sparse matrix data")
-    return x.contiguous()
+    """x against a prepared COO matrix: same checks, order and exception types as for the CSR entry points (the
+    reference's spmv_coo.py:232-249 repeats them)."""
+    from .spmv_csr import _validate_spmv_x
+
+    return _validate_spmv_x(x, prepared)
 
 
 def flagsparse_spmv_coo(data=None, row=None, col=None, x=None, shape=None, out=None, return_time=False,
@@ -238,7 +230,7 @@ def _prepare_spmm_coo_inputs(data, row, col, B, shape):
 
 def _resolve_spmm_coo_launch_config(n_dense_cols, nnz, block_n=None, block_nnz=256):
     """The reference's launch bookkeeping (spmm_coo.py:374-391); validated, not used by the kernels."""
-    warp_size, factor = _select_spmm_alg1_warp_and_factor(n_dense_cols)
+    warp_size, factor = _alg1_shape(n_dense_cols)
     if block_n is None:
         block_n = warp_size * factor
     if block_nnz is None:

@@ -2,7 +2,7 @@
 
 Same names, arguments, defaults, validation order and exception types as the reference's
 src/flagsparse/sparse_operations/spmm_csr.py (_prepare_spmm_csr_matrix :197-255,
-_prepare_spmm_csr_inputs :258-281, _resolve_spmm_alg1_launch_config :284-334, PreparedCsrSpmmOpt
+_prepare_spmm_csr_inputs :258-281, the launch-override checks :284-334, PreparedCsrSpmmOpt
 :337-392, prepare_spmm_csr_opt :480-522, flagsparse_spmm_csr :1057-1126, flagsparse_spmm_csr_opt
 :1129-1183).  Both entry points run the same nnz-tiled CUDA kernel; the reference's row-length buckets
 and its split workspace for rows over 2048 nnz are replaced by the tile plan and per-tile partial rows.
@@ -150,50 +150,39 @@ def _row_major(B):
     return B.contiguous()
 
 
-def _select_spmm_alg1_warp_and_factor(n_dense_cols):
-    """Tile-shape table of the reference (spmm_csr.py:284-296)."""
-    if n_dense_cols > 64:
-        return 32, 4
-    if n_dense_cols > 32:
-        return 32, 2
-    if n_dense_cols > 16:
-        return 32, 1
-    if n_dense_cols > 8:
-        return 16, 1
-    if n_dense_cols > 4:
-        return 8, 1
+# (dense columns above which the shape applies, lanes, column factor): the launch shapes the reference picks for its
+# base SpMM kernel (spmm_csr.py:284-296).  The CUDA kernel does not use them; they only give the defaults against
+# which explicit overrides are checked, and the bookkeeping dictionary callers may look at.
+_ALG1_SHAPES = ((64, 32, 4), (32, 32, 2), (16, 32, 1), (8, 16, 1), (4, 8, 1))
+
+
+def _alg1_shape(n_dense_cols):
+    for above, lanes, factor in _ALG1_SHAPES:
+        if n_dense_cols > above:
+            return lanes, factor
     return 4, 1
 
 
-def _resolve_spmm_alg1_launch_config(n_dense_cols, max_row_nnz, block_n=None, block_nnz=None, max_segments=None):
-    """Validate the launch overrides the way the reference does (spmm_csr.py:299-334).  The CUDA kernel
-    ignores the resulting numbers; the function exists so that bad overrides raise the same ValueError,
-    including the one for a max_segments too small for the longest row."""
-    warp_size, factor = _select_spmm_alg1_warp_and_factor(n_dense_cols)
-    if block_n is None:
-        block_n = warp_size * factor
-    if block_nnz is None:
-        block_nnz = warp_size
-    if block_n <= 0 or block_nnz <= 0:
-        raise ValueError("block_n and block_nnz must be positive when provided")
-    if max_segments is not None and max_segments <= 0:
-        raise ValueError("max_segments must be positive when provided")
-    required_segments = -(-max_row_nnz // block_nnz) if max_row_nnz > 0 else 0
-    if max_segments is not None and required_segments > int(max_segments):
-        raise ValueError(
-            "row nnz requires more CSR segments than the explicit max_segments override allows: "
-            f"required {required_segments}, provided {int(max_segments)}"
-        )
-    return {
-        "block_n": int(block_n),
-        "block_nnz": int(block_nnz),
-        "max_segments": (None if max_segments is None else int(max_segments)),
-        "required_segments": int(required_segments),
-        "warp_size": int(warp_size),
-        "factor": int(factor),
-        "max_row_nnz": int(max_row_nnz),
-        "auto_max_segments": max_segments is None,
-    }
+def _check_launch_overrides(n_dense_cols, max_row_nnz, block_n=None, block_nnz=None, max_segments=None):
+    """The two ways a call can be refused for its launch overrides, as in the reference (spmm_csr.py:299-334): a
+    non-positive block size or segment count, and a max_segments that cannot hold the longest row.  Returns the
+    reference's bookkeeping for the accepted values."""
+    lanes, factor = _alg1_shape(n_dense_cols)
+    tile_cols = lanes * factor if block_n is None else block_n
+    seg_len = lanes if block_nnz is None else block_nnz
+    if min(tile_cols, seg_len) <= 0:
+        raise ValueError("block_n and block_nnz, when given, must be positive")
+    needed = -(-max_row_nnz // seg_len) if max_row_nnz > 0 else 0
+    if max_segments is not None:
+        if max_segments <= 0:
+            raise ValueError("max_segments, when given, must be positive")
+        if needed > int(max_segments):
+            raise ValueError(f"the longest row needs {needed} segments of {seg_len} entries; max_segments allows "
+                             f"{int(max_segments)}")
+    return {"block_n": int(tile_cols), "block_nnz": int(seg_len),
+            "max_segments": None if max_segments is None else int(max_segments), "required_segments": int(needed),
+            "warp_size": int(lanes), "factor": int(factor), "max_row_nnz": int(max_row_nnz),
+            "auto_max_segments": max_segments is None}
 
 
 def _select_spmm_opt_block_n(n_dense_cols):
@@ -461,7 +450,7 @@ def flagsparse_spmm_csr(data, indices, indptr, B, shape, block_n=None, block_nnz
     prepared = prepare_spmm_csr_opt(data, indices, indptr, shape)
     B = _check_spmm_dense(B, prepared.data, prepared.n_cols)
     n_dense_cols = int(B.shape[1])
-    _resolve_spmm_alg1_launch_config(n_dense_cols, prepared.max_row_nnz, block_n=block_n, block_nnz=block_nnz,
+    _check_launch_overrides(n_dense_cols, prepared.max_row_nnz, block_n=block_n, block_nnz=block_nnz,
                                      max_segments=max_segments)
     if out is not None:
         _check_out(out, prepared.data.device, (prepared.n_rows, n_dense_cols), prepared.data.dtype,

@@ -143,19 +143,19 @@ def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
     function of this name (spmv_csr.py:379-436).  Returns (data, kernel_indices, kernel_indptr, n_rows,
     n_cols, stats)."""
     if not all(torch.is_tensor(t) for t in (data, indices, indptr)):
-        raise TypeError("data, indices, indptr must all be torch.Tensor")
+        raise TypeError("data, indices and indptr have to be torch.Tensor objects")
     if data.ndim != 1 or indices.ndim != 1 or indptr.ndim != 1:
-        raise ValueError("data, indices, indptr must be 1D tensors")
+        raise ValueError("data, indices and indptr have to be one-dimensional")
     n_rows, n_cols = int(shape[0]), int(shape[1])
     if indptr.numel() != n_rows + 1:
-        raise ValueError(f"indptr length must be n_rows+1={n_rows + 1}, got {indptr.numel()}")
+        raise ValueError(f"indptr has {indptr.numel()} entries, {n_rows} rows need {n_rows + 1}")
     if data.numel() != indices.numel():
-        raise ValueError("data and indices must have the same length (nnz)")
+        raise ValueError(f"{data.numel()} values but {indices.numel()} column indices")
     if not all(t.is_cuda for t in (data, indices, indptr)):
-        raise ValueError("data, indices, indptr must be CUDA tensors")
+        raise ValueError("data, indices and indptr have to live on a CUDA device")
     _check_value_dtype(data.dtype)
     if indices.dtype not in SUPPORTED_INDEX_DTYPES:
-        raise TypeError("indices dtype must be torch.int32 or torch.int64")
+        raise TypeError(f"indices are {indices.dtype}; int32 or int64 is needed")
 
     data = data.contiguous()
     indices = indices.contiguous()
@@ -167,14 +167,14 @@ def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
     nnz = data.numel()
     stats = _analyze_csr(indices, indptr, n_rows)
     if stats.ptr_first != 0:
-        raise ValueError("indptr must start at zero")
+        raise ValueError("indptr[0] is not 0")
     if stats.ptr_last != nnz:
-        raise ValueError("indptr[-1] must equal nnz")
+        raise ValueError(f"indptr[-1] is {stats.ptr_last}, the arrays hold {nnz} entries")
     if stats.n_decreasing > 0:
-        raise ValueError("indptr must be non-decreasing")
+        raise ValueError("indptr decreases somewhere")
     if nnz > 0:
         if stats.min_index < 0 or stats.max_index >= n_cols:
-            raise IndexError("indices out of range for n_cols")
+            raise IndexError(f"column indices span [{stats.min_index}, {stats.max_index}], the matrix has {n_cols} columns")
         if stats.max_index > _INDEX_LIMIT_INT32:
             raise ValueError(f"int64 column index {stats.max_index} exceeds the int32 kernel range")
     # same narrowing as the reference (:422-425): 32-bit column indices always, 32-bit indptr when it fits
@@ -184,19 +184,20 @@ def _prepare_spmv_csr_matrix(data, indices, indptr, shape):
 
 
 def _validate_spmv_x(x, prepared):
-    """Checks of the reference's _validate_spmv_x (spmv_csr.py:439-452), same order."""
-    if x is None or not torch.is_tensor(x):
-        raise TypeError("x must be a torch.Tensor")
-    if x.ndim != 1:
-        raise ValueError("x must be a 1D tensor")
-    if not x.is_cuda:
-        raise ValueError("x must be a CUDA tensor")
-    if x.dtype != prepared.data.dtype:
-        raise TypeError("x dtype must match sparse matrix dtype")
-    if x.numel() != prepared.n_cols:
-        raise ValueError(f"x length must be n_cols={prepared.n_cols}, got {x.numel()}")
-    if x.device != prepared.data.device:
-        raise ValueError("x must be on the same device as sparse matrix data")
+    """x against a prepared matrix: the checks of the reference's _validate_spmv_x (spmv_csr.py:439-452) in its
+    order, each with the exception type it raises there.  Returns x, contiguous."""
+    if not torch.is_tensor(x):            # None included
+        raise TypeError("x has to be a torch.Tensor")
+    a = prepared.data
+    for failed, exc, why in (
+        (x.ndim != 1, ValueError, "x has to be one-dimensional"),
+        (not x.is_cuda, ValueError, "x has to live on a CUDA device"),
+        (x.dtype != a.dtype, TypeError, f"x is {x.dtype}, the matrix holds {a.dtype}"),
+        (x.numel() != prepared.n_cols, ValueError, f"x has {x.numel()} elements, the matrix {prepared.n_cols} columns"),
+        (x.device != a.device, ValueError, f"x is on {x.device}, the matrix on {a.device}"),
+    ):
+        if failed:
+            raise exc(why)
     return x.contiguous()
 
 
@@ -374,31 +375,24 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
 # ---------------------------------------------------------------------------------------------------
 # COO front-end: convert to CSR, then the same kernels (reference: spmv_csr.py:613-758)
 # ---------------------------------------------------------------------------------------------------
-def _coo_is_sorted_lex(row_i64, col_i64, n_cols):
-    """True iff the COO entries are in non-decreasing (row, col) order (reference :613-620)."""
-    n = row_i64.numel()
-    if n <= 1:
-        return True
-    key = row_i64 * max(1, int(n_cols)) + col_i64
-    return bool((key[1:] >= key[:-1]).all().item())
-
-
 def coo_to_csr_for_spmv(data, row, col, shape, assume_sorted=False):
-    """COO -> (data, int32 column indices, int64 indptr), sorting by (row, col) when needed
-    (reference :623-647)."""
+    """COO triple -> (values, int32 column indices, int64 row pointer) with the entries in (row, column) order,
+    which is what the reference's function of this name returns (spmv_csr.py:623-647).  Entries already in order
+    (or declared so) are not touched; otherwise one sort on the combined key.  The row pointer is read off
+    the ordered row ids by binary search."""
     n_rows, n_cols = int(shape[0]), int(shape[1])
-    row64 = row.to(torch.int64)
-    col64 = col.to(torch.int64)
-    if row64.numel() == 0:
-        return data, col64.to(torch.int32), torch.zeros(n_rows + 1, dtype=torch.int64, device=data.device)
-    if assume_sorted or _coo_is_sorted_lex(row64, col64, n_cols):
-        row_s, col_s, data_s = row64, col64, data
-    else:
-        order = torch.argsort(row64 * max(1, n_cols) + col64)
-        row_s, col_s, data_s = row64[order], col64[order], data[order]
-    indptr = torch.zeros(n_rows + 1, dtype=torch.int64, device=data.device)
-    indptr[1:] = torch.cumsum(torch.bincount(row_s, minlength=n_rows), dim=0)
-    return data_s, col_s.to(torch.int32), indptr
+    dev = data.device
+    rows, cols = row.to(torch.int64), col.to(torch.int64)
+    if rows.numel() == 0:
+        return data, cols.to(torch.int32), torch.zeros(n_rows + 1, dtype=torch.int64, device=dev)
+    if not assume_sorted and rows.numel() > 1:
+        key = rows * max(1, n_cols) + cols
+        if bool((key[1:] < key[:-1]).any()):
+            order = torch.argsort(key)     # entries with one (row, column) keep the order torch's default sort gives
+            rows, cols, data = rows[order], cols[order], data[order]
+        del key
+    indptr = torch.searchsorted(rows.contiguous(), torch.arange(n_rows + 1, dtype=torch.int64, device=dev))
+    return data, cols.to(torch.int32), indptr
 
 
 def _check_coo_triple(data, row, col, extra=()):

@@ -66,11 +66,11 @@ def test_spmv_validation_on_cpu_tensors():
         fs.flagsparse_spmv_csr(data, indices, None, x, (2, 2))
     with pytest.raises(TypeError):
         fs.flagsparse_spmv_csr([1.0], indices, indptr, x, (2, 2))
-    with pytest.raises(ValueError, match="1D"):
+    with pytest.raises(ValueError, match="one-dimensional"):
         fs.flagsparse_spmv_csr(data.reshape(1, 3), indices, indptr, x, (2, 2))
-    with pytest.raises(ValueError, match="indptr length"):
+    with pytest.raises(ValueError, match="indptr has 2 entries"):
         fs.flagsparse_spmv_csr(data, indices, indptr[:-1], x, (2, 2))
-    with pytest.raises(ValueError, match="same length"):
+    with pytest.raises(ValueError, match="2 values but 3 column indices"):
         fs.flagsparse_spmv_csr(data[:2], indices, indptr, x, (2, 2))
     # CPU tensors are refused exactly where the reference refuses them: no silent CPU path
     with pytest.raises(ValueError, match="CUDA"):
@@ -129,7 +129,7 @@ def test_alg1_launch_config_matches_reference():
     for case in golden_index()["host"]["alg1"]:
         want = case["result"]
         try:
-            got = spmm_csr._resolve_spmm_alg1_launch_config(case["n"], case["max_row_nnz"], **case["kw"])
+            got = spmm_csr._check_launch_overrides(case["n"], case["max_row_nnz"], **case["kw"])
         except Exception as exc:
             got = {"raises": type(exc).__name__}
         assert got == want, case
