@@ -32,6 +32,7 @@ RUNS_MIN_MEAN = 1.5
 FLAG_DEBUG_TIMEOUT = 256    # FSB_PANEL_DEBUG_TIMEOUT
 MAX_ROW_NNZ = 512
 MIN_NNZ = 1 << 22
+ACC_BANKS = {4: 32, 8: 16}   # accumulators that sit in different shared-memory banks (32 banks of 4 bytes), by value size
 
 
 class PanelLayout:
@@ -163,7 +164,7 @@ def _cumsum0(counts):
 
 
 def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, rounds, max_slot_overhead,
-                n_buffers=2, pad_row=0xFFFF):
+                n_buffers=2, pad_row=0xFFFF, bank_sort=True):
     """Cut the entries of every unit (already in unit order, row-major inside a unit) into pieces of 32 * rounds
     slots and lay them out for the kernel.  acc_p: accumulator (local row) of each entry; run_key_p: entries that
     follow each other with the same key inside one unit form a run, which must not straddle two pieces; pad_row:
@@ -211,6 +212,14 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     if max_slot_overhead is not None and n_pieces * SLOTS > max_slot_overhead * nnz + 4096:
         return None
     piece = torch.searchsorted(piece_start, ar, right=True) - 1
+    if bank_sort:
+        # Inside a piece, order the entries by the shared-memory bank of their accumulator (a stable sort: the rows
+        # of one bank stay in row order and the entries of a row stay together, so every rule above still holds).
+        # A round takes every `rounds`-th entry of that order, so the 32 accumulators of a round spread over the
+        # banks instead of falling on them at random (about two instead of 3.5 passes per shared-memory access).
+        order = torch.sort(piece * 32 + (acc_p % ACC_BANKS[sv]), stable=True).indices
+        data_p, acc_p, cols_p, unit_of_entry = data_p[order], acc_p[order], cols_p[order], unit_of_entry[order]
+        del order
     slot = ar - piece_start[piece]
     # inside a piece, slot = rounds * lane + k; both arrays are interleaved so that each 128-bit load of a warp is
     # contiguous: values at (k // E) * 32 * E + lane * E + k % E (E = values per 16 bytes), words with E = 4

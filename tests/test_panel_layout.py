@@ -55,7 +55,11 @@ def _evaluate(lay, x, n_rows, n_cols, slots):
                 assert live.any() and np.all(live[:live.sum()])            # real slots first, then padding
                 assert np.all(vals[~live] == 0)
                 rl, fl = rloc[live], field[live]
-                assert np.all(fl // CW == parity) and np.all(np.diff(rl) >= 0)
+                assert np.all(fl // CW == parity)
+                # ordered by the shared-memory bank of the accumulator, rows ascending inside a bank, and the
+                # entries of a row next to each other
+                banks = panel.ACC_BANKS[lay.val.element_size()]
+                assert np.all(np.diff((rl % banks) * (1 << 20) + rl) >= 0)
                 cols = uch[u] * CW + fl % CW
                 rows = b * RB + rl
                 assert np.all(rows < n_rows) and np.all(cols < n_cols)
