@@ -12,6 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "libfsb.so")
 
 FSB_F32, FSB_F64 = 0, 1
+FSB_F16, FSB_BF16, FSB_C64, FSB_C128 = 2, 3, 4, 5     # fsb_spmv_csr_wide only
 FSB_I32, FSB_I64 = 0, 1
 FSB_SPMV_AUTO, FSB_SPMV_VECTOR, FSB_SPMV_STREAM = 0, 1, 2
 FSB_SPMV_PANEL = 3  # host-side tag only: the panel kernel has its own entry point
@@ -57,6 +58,8 @@ SIGNATURES = {
         _i32,
         [_i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _sz, _vp, _vp],
     ),
+    "fsb_spmv_csr_wide": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "fsb_spmm_csr_wide": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "fsb_sddmm_csr": (_i32, [_i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double,
                              _c.c_double, _vp]),
 }

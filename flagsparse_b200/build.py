@@ -12,7 +12,7 @@ import sys
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 INCLUDE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
 LIB = os.path.join(CSRC, "libfsb.so")
-SOURCES = ("csr_analyze.cu", "spmv_csr.cu", "spmv_panel.cu", "spmm_csr.cu", "sddmm_csr.cu")
+SOURCES = ("csr_analyze.cu", "spmv_csr.cu", "spmv_panel.cu", "spmv_wide.cu", "spmm_csr.cu", "sddmm_csr.cu")
 NVCC_FLAGS = (
     "-O3",
     "-std=c++17",

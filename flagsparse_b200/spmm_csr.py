@@ -237,7 +237,7 @@ class PreparedCsrSpmmOpt:
         self._whole = None       # the matrix as one _CsrPart (shares the tile plan)
         self._panels = {}        # number of column panels -> list of _CsrPart
         self._span = None        # columns spanned by a window of consecutive entries (median over samples)
-        # float16 / bfloat16 / complex values: (kind, prepared real matrices) the products go through (widetypes.py)
+        # float16 / bfloat16 / complex values: ("native", []) -- the product goes through fsb_spmm_csr_wide
         self.wide = wide
 
     @property
@@ -339,11 +339,9 @@ def prepare_spmm_csr_opt(data, indices, indptr, shape):
     )
     nnz = data.numel()
     if data.dtype in widetypes.WIDE_DTYPES:
-        # computed in a wider real type, as the reference's base path does (:525-560): one real matrix per part
-        kind, reals = widetypes.split_values(data)
-        parts = [prepare_spmm_csr_opt(r, kernel_indices, kernel_indptr, shape) for r in reals]
-        return PreparedCsrSpmmOpt(data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats,
-                                  parts[0].tile_nnz, None, wide=(kind, parts))
+        # read as stored by fsb_spmm_csr_wide: nothing to plan, no second copy of the matrix
+        return PreparedCsrSpmmOpt(data, kernel_indices, kernel_indptr, shape, n_rows, n_cols, stats, 0, None,
+                                  wide=("native", []))
     tile_nnz, tile_row = 0, None
     if nnz > 0 and n_rows > 0:
         tile_nnz = int(_lib.lib().fsb_spmm_tile_nnz(_VTYPE[data.dtype]))
@@ -392,16 +390,34 @@ def _check_out(out, device, shape, dtype, device_msg):
         raise ValueError("out shape/dtype must match result")
 
 
+def _spmm_launch_wide(prepared, B, C):
+    """Enqueue C = A B for float16 / bfloat16 / complex values (fsb_spmm_csr_wide): B and C are float32 for the half
+    precisions and of the matrix's own type for complex values; B may have any row stride.  Stands in for the
+    reference's base launch helper on these types (_triton_spmm_csr_impl, spmm_csr.py:525-599)."""
+    from .spmv_csr import _WIDE_VTYPE
+
+    p = prepared
+    dev = p.data.device
+    if p.n_rows == 0 or B.shape[1] == 0:
+        return
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fsb_spmm_csr_wide(
+            _WIDE_VTYPE[p.data.dtype], _ITYPE[p.kernel_indptr.dtype], _ptr(p.data), _ptr(p.kernel_indices),
+            p.kernel_indptr.data_ptr(), _ptr(B), B.stride(0) if B.shape[0] > 1 else B.shape[1], _ptr(C), C.stride(0),
+            p.n_rows, p.n_cols, int(B.shape[1]), p.data.numel(), _stream_ptr(dev),
+        )
+    _lib.check(rc, "fsb_spmm_csr_wide")
+
+
 def _run_spmm(prepared, B, out, return_time):
     dev, dtype = prepared.data.device, prepared.data.dtype
     shape = (prepared.n_rows, int(B.shape[1]))
     if prepared.wide is not None:
-        kind, parts = prepared.wide
         t0 = None
         if return_time:
             torch.cuda.synchronize(dev)
             t0 = time.perf_counter()
-        C = widetypes.product(kind, parts, B, _spmm_launch, shape, dtype)
+        C = widetypes.run(prepared, B, _spmm_launch_wide, shape)
         elapsed_ms = None
         if return_time:
             torch.cuda.synchronize(dev)

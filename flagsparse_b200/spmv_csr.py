@@ -112,7 +112,7 @@ class PreparedCsrSpmv:
         self.scratch = scratch
         self.panel = panel
         self.long_rows = long_rows   # (prepared short-row part, LongRowLayout) when the long rows were split off
-        # float16 / bfloat16 / complex values: (kind, prepared real matrices) the products go through (widetypes.py)
+        # float16 / bfloat16 / complex values: ("native", []) -- the product goes through fsb_spmv_csr_wide
         self.wide = wide
         n_tiles = 0 if tile_row is None else tile_row.numel() - 1
         kind = {_lib.FSB_SPMV_STREAM: "stream", _lib.FSB_SPMV_PANEL: "panel"}.get(algo, "vector")
@@ -237,15 +237,13 @@ def _prepare_spmv_csr(data, indices, indptr, shape, block_nnz, max_segments, reu
     block_nnz_use, max_segments_use = _resolve_block_nnz(max_row_nnz, block_nnz, max_segments)
     nnz = data.numel()
     if data.dtype in widetypes.WIDE_DTYPES:
-        # the reference computes these in a wider real type too (:496-535); one prepared real matrix per part
-        kind, reals = widetypes.split_values(data)
-        parts = [_prepare_spmv_csr(r, kernel_indices, kernel_indptr, shape, block_nnz, max_segments, reuse_expected,
-                                   allow_split) for r in reals]
+        # float16 / bfloat16 / complex values are read as they are stored by a kernel of their own (fsb_spmv_csr_wide):
+        # nothing to plan, no second copy of the matrix
         return PreparedCsrSpmv(
             data=data, kernel_indices=kernel_indices, kernel_indptr=kernel_indptr, shape=shape, n_rows=n_rows,
             n_cols=n_cols, block_nnz=block_nnz_use, max_segments=max_segments_use, max_row_nnz=max_row_nnz,
-            stats=stats, algo=parts[0].algo, tuning=parts[0].tuning, tile_nnz=parts[0].tile_nnz, tile_row=None,
-            scratch=None, wide=(kind, parts),
+            stats=stats, algo=_lib.FSB_SPMV_VECTOR, tuning=0, tile_nnz=0, tile_row=None, scratch=None,
+            wide=("native", []),
         )
     algo = _select_spmv_algo(n_rows, nnz, max_row_nnz)
     tuning = int(os.environ.get("FSB_SPMV_TUNING", "0"))
@@ -317,6 +315,26 @@ def _spmv_launch(prepared, x, y):
     _lib.check(rc, "fsb_spmv_csr")
 
 
+_WIDE_VTYPE = {torch.float16: _lib.FSB_F16, torch.bfloat16: _lib.FSB_BF16, torch.complex64: _lib.FSB_C64,
+               torch.complex128: _lib.FSB_C128}
+
+
+def _spmv_launch_wide(prepared, x, y):
+    """Enqueue y = A x for float16 / bfloat16 / complex values (fsb_spmv_csr_wide): x and y are float32 for the
+    half precisions and of the matrix's own type for complex values.  Stands in for the reference's base launch
+    helper on these types (_triton_spmv_csr_impl_prepared, :510-554)."""
+    p = prepared
+    dev = p.data.device
+    if p.n_rows == 0:
+        return
+    with torch.cuda.device(dev):
+        rc = _lib.lib().fsb_spmv_csr_wide(
+            _WIDE_VTYPE[p.data.dtype], _ITYPE[p.kernel_indptr.dtype], _ptr(p.data), _ptr(p.kernel_indices),
+            p.kernel_indptr.data_ptr(), _ptr(x), _ptr(y), p.n_rows, p.n_cols, p.data.numel(), _stream_ptr(dev),
+        )
+    _lib.check(rc, "fsb_spmv_csr_wide")
+
+
 def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None, block_nnz=256,
                         max_segments=None, out=None, return_time=False, use_opt=False, prepared=None):
     """CSR SpMV: y = A @ x (reference: spmv_csr.py:557-610, same arguments and defaults).
@@ -336,17 +354,15 @@ def flagsparse_spmv_csr(data=None, indices=None, indptr=None, x=None, shape=None
     if out is not None and (out.shape != (prepared.n_rows,) or out.dtype != dtype):
         raise ValueError("out shape/dtype must match result")
     if prepared.wide is not None:
-        kind, parts = prepared.wide
         t0 = None
         if return_time:
             torch.cuda.synchronize(dev)
             t0 = time.perf_counter()
-        y = widetypes.product(kind, parts, x, _spmv_launch, (prepared.n_rows,), dtype)
+        y = widetypes.run(prepared, x, _spmv_launch_wide, (prepared.n_rows,))
         elapsed_ms = None
         if return_time:
             torch.cuda.synchronize(dev)
             elapsed_ms = (time.perf_counter() - t0) * 1000.0
-            prepared.check_status()
         if out is not None:
             out.copy_(y)
             y = out

@@ -1,17 +1,16 @@
-"""float16, bfloat16, complex64 and complex128 values through the float32 / float64 kernels.
+"""float16, bfloat16, complex64 and complex128 values: the host side of fsb_spmv_csr_wide / fsb_spmm_csr_wide.
 
 The reference's base paths take these four value types by computing in a wider real type and casting back:
 half precisions run its float32 kernel on `data.to(float32)` and `x.to(float32)` and round the result
 (src/flagsparse/sparse_operations/spmv_csr.py:496-535, spmm_csr.py:525-560 of the reference), complex values run a
-kernel over the interleaved real view (spmv_csr.py:123-155, 536-554; spmm_csr.py:138-195).  Here the same results
-come from the real kernels of this package without new device code:
-  * float16 / bfloat16: one float32 copy of the values made at prepare time, x (or B) widened per call, the
-    float32 result rounded once to the caller's type;
-  * complex: the values split into a real and an imaginary matrix at prepare time (same indices), and
-        Re y = A_re x_re - A_im x_im,   Im y = A_re x_im + A_im x_re
-    as four real products per call, in the component precision (float32 for complex64, float64 for complex128).
-The functions below hold the arithmetic only; the caller passes `launch(part, operand, result)`, which is the CUDA
-launch in the package and a host stand-in in the tests of this module.
+kernel over the interleaved real view (spmv_csr.py:123-155, 536-554; spmm_csr.py:138-195).  Here one kernel per
+product reads the matrix as it is stored (2 bytes per half-precision value, interleaved pairs for complex values):
+  * float16 / bfloat16: the dense operand is widened to float32 once per call, products and sums are float32, the
+    float32 result is rounded once to the caller's type;
+  * complex: operand and result stay in the caller's type.
+`dense_dtype` says which type the kernel's dense operand and result have; `run` does the widening, the launch and
+the rounding around a caller-supplied `launch(prepared, dense operand, dense result)`, which is the CUDA launch in
+the package and a host stand-in in the CPU tests.
 """
 
 import torch
@@ -21,47 +20,23 @@ COMPLEX_DTYPES = (torch.complex64, torch.complex128)
 WIDE_DTYPES = HALF_DTYPES + COMPLEX_DTYPES
 
 
-def compute_dtype(dtype):
-    """The real type the kernels run in for values of `dtype`."""
+def dense_dtype(dtype):
+    """Type of the dense operand and of the result as the kernel sees them, for matrix values of `dtype`."""
     if dtype in HALF_DTYPES:
         return torch.float32
-    if dtype == torch.complex64:
-        return torch.float32
-    if dtype == torch.complex128:
-        return torch.float64
-    return dtype
+    if dtype in COMPLEX_DTYPES:
+        return dtype
+    raise TypeError(f"{dtype} has kernels of its own")
 
 
-def split_values(data):
-    """(kind, real value arrays) of a value array: ('cast', [float32 copy]) or ('complex', [re, im])."""
-    if data.dtype in HALF_DTYPES:
-        return "cast", [data.to(torch.float32)]
-    if data.dtype in COMPLEX_DTYPES:
-        ri = torch.view_as_real(data.contiguous())
-        return "complex", [ri[..., 0].contiguous(), ri[..., 1].contiguous()]
-    raise TypeError(f"{data.dtype} needs no widening")
-
-
-def _split_operand(v):
-    ri = torch.view_as_real(v.contiguous())
-    return ri[..., 0].contiguous(), ri[..., 1].contiguous()
-
-
-def product(kind, parts, operand, launch, out_shape, dtype):
-    """A @ operand for a matrix held as `parts` (see split_values); operand is x (1-D) or B (2-D) of the caller's
-    dtype.  launch(part, real operand, real result) must fill `result` with part @ operand."""
-    dev = operand.device
-    comp = compute_dtype(dtype)
-    if kind == "cast":
-        y = torch.empty(out_shape, dtype=comp, device=dev)
-        launch(parts[0], operand.to(comp).contiguous(), y)
-        return y.to(dtype)
-    if kind == "complex":
-        o_re, o_im = _split_operand(operand)
-        t = [torch.empty(out_shape, dtype=comp, device=dev) for _ in range(4)]
-        launch(parts[0], o_re, t[0])
-        launch(parts[1], o_im, t[1])
-        launch(parts[0], o_im, t[2])
-        launch(parts[1], o_re, t[3])
-        return torch.complex(t[0] - t[1], t[2] + t[3])
-    raise ValueError(f"unknown kind {kind!r}")
+def run(prepared, operand, launch, out_shape):
+    """prepared.data @ operand for a matrix of one of the four types; operand is x (1-D) or B (2-D, unit stride
+    along a row) of the matrix's dtype.  Returns a new tensor of that dtype."""
+    dtype = prepared.data.dtype
+    dense = dense_dtype(dtype)
+    o = operand if operand.dtype == dense else operand.to(dense)
+    if o.ndim == 1 or o.stride(-1) != 1 or (o.shape[0] > 1 and o.stride(0) < o.shape[1]):
+        o = o.contiguous()
+    result = torch.empty(out_shape, dtype=dense, device=operand.device)
+    launch(prepared, o, result)
+    return result if dense == dtype else result.to(dtype)

@@ -33,6 +33,10 @@ extern "C" {
 /* dtype tags */
 #define FSB_F32 0
 #define FSB_F64 1
+#define FSB_F16 2             /* fsb_spmv_csr_wide / fsb_spmm_csr_wide only */
+#define FSB_BF16 3
+#define FSB_C64 4             /* interleaved (re, im) float32 pairs */
+#define FSB_C128 5            /* interleaved (re, im) float64 pairs */
 #define FSB_I32 0
 #define FSB_I64 1
 
@@ -239,6 +243,26 @@ int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, const void* 
                  const void* indptr, const void* B, int64_t ldb, void* C, int64_t ldc, int64_t n_rows,
                  int64_t n_cols, int64_t n_dense, int64_t nnz, int algo, const int32_t* tile_row,
                  void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+
+/*
+ * y = A x for float16, bfloat16, complex64 and complex128 values, read as they are stored (no widened or split copy of
+ * the matrix).  vtype FSB_F16 / FSB_BF16: data holds 2-byte values, x and y are float32 (the caller widens x and rounds
+ * y once per call, which is what the reference's base path computes: spmv_csr.py:496-535 with the kernel :94-120 on
+ * float32 copies); products and sums in float32.  vtype FSB_C64 / FSB_C128: data, x and y hold interleaved (re, im)
+ * pairs of float32 / float64; replaces the launch of _spmv_csr_complex_kernel (spmv_csr.py:123-155, 536-554).
+ * indices are int32, indptr int32 or int64 (ptype).  One launch, no scratch, bit-reproducible.
+ */
+int fsb_spmv_csr_wide(int vtype, int ptype, const void* data, const int32_t* indices, const void* indptr,
+                      const void* x, void* y, int64_t n_rows, int64_t n_cols, int64_t nnz, void* stream);
+
+/*
+ * C = A B for the same four value types, with the same conventions (B and C float32 for the half precisions, of the
+ * matrix's own interleaved type for complex values; row-major with leading dimensions ldb / ldc in elements of that
+ * type).  Replaces the launch in _triton_spmm_csr_impl for these types (spmm_csr.py:525-599, complex kernel :138-195).
+ */
+int fsb_spmm_csr_wide(int vtype, int ptype, const void* data, const int32_t* indices, const void* indptr,
+                      const void* B, int64_t ldb, void* C, int64_t ldc, int64_t n_rows, int64_t n_cols,
+                      int64_t n_dense, int64_t nnz, void* stream);
 
 /*
  * Sampled dense-dense product on a CSR pattern: out[p] = alpha * dot(X[row(p), :], Y[indices[p], :]) + beta * data[p]

@@ -59,6 +59,31 @@ class Launches:
         if prepared.n_rows:
             y.copy_(torch.from_numpy(np.asarray(_matrix(prepared) @ x.numpy(), dtype=x.numpy().dtype)))
 
+    def spmv_launch_wide(self, prepared, x, y):
+        """Stand-in for fsb_spmv_csr_wide: the matrix as stored, x and y float32 (half precisions) or complex."""
+        dt = prepared.data.dtype
+        half = dt in (torch.float16, torch.bfloat16)
+        assert dt in (torch.float16, torch.bfloat16, torch.complex64, torch.complex128)
+        assert x.dtype == y.dtype == (torch.float32 if half else dt) and x.is_contiguous() and y.is_contiguous()
+        self.spmv.append("wide")
+        vals = prepared.data.to(torch.float32 if half else dt).numpy()
+        a = sp.csr_matrix((vals, prepared.kernel_indices.numpy(), prepared.kernel_indptr.numpy()),
+                          shape=(prepared.n_rows, prepared.n_cols))
+        if prepared.n_rows:
+            y.copy_(torch.from_numpy(np.asarray(a @ x.numpy(), dtype=x.numpy().dtype)))
+
+    def spmm_launch_wide(self, prepared, B, C):
+        """Stand-in for fsb_spmm_csr_wide."""
+        dt = prepared.data.dtype
+        half = dt in (torch.float16, torch.bfloat16)
+        assert B.dtype == C.dtype == (torch.float32 if half else dt) and B.stride(-1) == 1
+        self.spmm.append(("wide", int(B.shape[1])))
+        vals = prepared.data.to(torch.float32 if half else dt).numpy()
+        a = sp.csr_matrix((vals, prepared.kernel_indices.numpy(), prepared.kernel_indptr.numpy()),
+                          shape=(prepared.n_rows, prepared.n_cols))
+        if prepared.n_rows and B.shape[1]:
+            C.copy_(torch.from_numpy(np.asarray(a @ B.numpy(), dtype=B.numpy().dtype)))
+
     def spmm_launch(self, prepared, B, C):
         assert prepared.data.dtype in (torch.float32, torch.float64)
         assert B.dtype == prepared.data.dtype == C.dtype and C.shape == (prepared.n_rows, B.shape[1])
@@ -77,8 +102,10 @@ def fake_cuda():
         mock.patch.object(spmv_csr, "_tile_plan", fake_tile_plan),
         mock.patch.object(spmm_csr, "_tile_plan", fake_tile_plan),
         mock.patch.object(spmv_csr, "_spmv_launch", launches.spmv_launch),
+        mock.patch.object(spmv_csr, "_spmv_launch_wide", launches.spmv_launch_wide),
         mock.patch.object(coo, "_spmv_launch", launches.spmv_launch),
         mock.patch.object(spmm_csr, "_spmm_launch", launches.spmm_launch),
+        mock.patch.object(spmm_csr, "_spmm_launch_wide", launches.spmm_launch_wide),
         mock.patch.object(torch.cuda, "synchronize", lambda *a, **k: None),
     ]
     for p in patches:

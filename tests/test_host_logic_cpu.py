@@ -133,20 +133,20 @@ def test_coo_and_wide_dtype_paths(fsb_lib):
         p = fs.prepare_spmv_coo(T(val), T(row), T(col), (30, 20))
         assert p.use_seg_kernel and p.n_segs == np.unique(row).size
         assert torch.allclose(fs.flagsparse_spmv_coo(x=T(x), prepared=p), y, rtol=0, atol=1e-5)
-        # complex values: two real matrices, four real products
+        # complex values: one launch of the kernel that reads them as stored
         launches.spmv.clear()
         cval = torch.from_numpy(val[order] + 1j * rng.uniform(-1, 1, 400)).to(torch.complex64)
         cx = torch.from_numpy(x + 1j * rng.uniform(-1, 1, 20)).to(torch.complex64)
         cy = fs.flagsparse_spmv_csr(cval, T(col[order]), T(indptr), cx, (30, 20))
-        assert len(launches.spmv) == 4 and cy.dtype == torch.complex64
+        assert launches.spmv == ["wide"] and cy.dtype == torch.complex64
         import scipy.sparse as sp
 
         ref = sp.csr_matrix((cval.numpy(), col[order], indptr), shape=(30, 20)) @ cx.numpy()
         assert np.allclose(cy.numpy(), ref, rtol=0, atol=1e-4)
-        # half precision: one float32 product, rounded once
+        # half precision: one launch on the 2-byte values, x widened and y rounded once
         launches.spmv.clear()
         hy = fs.flagsparse_spmv_csr(T(val[order]).half(), T(col[order]), T(indptr), T(x).half(), (30, 20))
-        assert launches.spmv == ["vector"] and hy.dtype == torch.float16
+        assert launches.spmv == ["wide"] and hy.dtype == torch.float16
 
 
 def test_mtx_batch_through_the_real_prepare(fsb_lib):

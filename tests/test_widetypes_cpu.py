@@ -1,19 +1,17 @@
-"""float16 / bfloat16 / complex values through real products (flagsparse_b200/widetypes.py), with a host stand-in
-for the CUDA launch: the arithmetic of the split and of the recombination, for a vector and for a dense block."""
+"""float16 / bfloat16 / complex values on CPU: the host side of the entry points (flagsparse_b200/widetypes.py:
+widening of the dense operand, one launch, one rounding) with host stand-ins for fsb_spmv_csr_wide /
+fsb_spmm_csr_wide, against exact products of the stored values and against outputs of the reference's own base
+paths (tests/golden/wide_*.npz)."""
 
 import numpy as np
 import pytest
 import scipy.sparse as sp
 import torch
 
+import flagsparse_b200 as fs
+from fake_device import fake_cuda
 from flagsparse_b200 import widetypes as W
 from helpers import handmade_csr
-
-
-def _launch(part, operand, result):
-    """Stand-in for the CUDA launch: part is a scipy matrix in the compute type."""
-    assert operand.is_contiguous() and operand.dtype == result.dtype
-    result.copy_(torch.from_numpy(np.asarray(part @ operand.numpy())))
 
 
 def _matrix(dtype, seed=1):
@@ -29,22 +27,23 @@ def _matrix(dtype, seed=1):
 
 @pytest.mark.parametrize("dtype", W.WIDE_DTYPES, ids=str)
 @pytest.mark.parametrize("n_dense", [None, 5])
-def test_product_through_real_parts(dtype, n_dense):
+def test_product_of_the_stored_values(dtype, n_dense, fsb_lib):
     vals, i, p, shape = _matrix(dtype)
-    kind, reals = W.split_values(vals)
-    comp = W.compute_dtype(dtype)
-    assert kind == ("cast" if dtype in W.HALF_DTYPES else "complex") and all(r.dtype == comp for r in reals)
-    assert len(reals) == (1 if kind == "cast" else 2) and all(r.is_contiguous() for r in reals)
-    parts = [sp.csr_matrix((r.numpy(), i, p), shape=shape) for r in reals]
     rng = np.random.default_rng(7)
     oshape = (shape[1],) if n_dense is None else (shape[1], n_dense)
     if dtype in W.COMPLEX_DTYPES:
         operand = torch.from_numpy(rng.uniform(-1, 1, oshape) + 1j * rng.uniform(-1, 1, oshape)).to(dtype)
     else:
         operand = torch.from_numpy(rng.uniform(-1, 1, oshape)).to(dtype)
-    out_shape = (shape[0],) if n_dense is None else (shape[0], n_dense)
-    y = W.product(kind, parts, operand, _launch, out_shape, dtype)
-    assert y.dtype == dtype and tuple(y.shape) == out_shape
+    ti, tp = torch.from_numpy(i), torch.from_numpy(p)
+    with fake_cuda() as launches:
+        if n_dense is None:
+            y = fs.flagsparse_spmv_csr(vals, ti, tp, operand, shape)
+            assert launches.spmv == ["wide"]
+        else:
+            y = fs.flagsparse_spmm_csr(vals, ti, tp, operand, shape)
+            assert launches.spmm == [("wide", n_dense)]
+    assert y.dtype == dtype and tuple(y.shape) == ((shape[0],) if n_dense is None else (shape[0], n_dense))
     # reference: the same matrix and operand (as stored, i.e. after their own rounding) in the widest type
     wide = torch.complex128 if dtype in W.COMPLEX_DTYPES else torch.float64
     a = sp.csr_matrix((vals.to(wide).numpy(), i, p), shape=shape)
@@ -56,24 +55,37 @@ def test_product_through_real_parts(dtype, n_dense):
     assert not y.to(wide).numpy()[np.diff(p) == 0].any()          # empty rows stay exact zeros
 
 
-def test_half_precision_result_is_the_rounded_float32_result():
+def test_half_precision_result_is_the_rounded_float32_result(fsb_lib):
     vals, i, p, shape = _matrix(torch.float16)
-    kind, reals = W.split_values(vals)
-    part = sp.csr_matrix((reals[0].numpy(), i, p), shape=shape)
     x = torch.from_numpy(np.random.default_rng(3).uniform(-1, 1, shape[1])).to(torch.float16)
-    y = W.product(kind, [part], x, _launch, (shape[0],), torch.float16)
+    with fake_cuda():
+        y = fs.flagsparse_spmv_csr(vals, torch.from_numpy(i), torch.from_numpy(p), x, shape)
+    part = sp.csr_matrix((vals.to(torch.float32).numpy(), i, p), shape=shape)
     y32 = torch.from_numpy(np.asarray(part @ x.to(torch.float32).numpy()))
     assert torch.equal(y, y32.to(torch.float16))
 
 
-def test_native_types_are_not_split():
+def test_dense_types_and_strided_operands():
+    assert W.dense_dtype(torch.float16) == W.dense_dtype(torch.bfloat16) == torch.float32
+    assert W.dense_dtype(torch.complex64) == torch.complex64 and W.dense_dtype(torch.complex128) == torch.complex128
     for dt in (torch.float32, torch.float64):
-        assert W.compute_dtype(dt) == dt
         with pytest.raises(TypeError):
-            W.split_values(torch.ones(3, dtype=dt))
-    assert W.compute_dtype(torch.complex128) == torch.float64 and W.compute_dtype(torch.bfloat16) == torch.float32
-    with pytest.raises(ValueError):
-        W.product("other", [], torch.ones(2), _launch, (2,), torch.float32)
+            W.dense_dtype(dt)
+
+    class P:
+        data = torch.ones(2, dtype=torch.complex64)
+
+    seen = []
+
+    def launch(prepared, o, r):
+        seen.append((o.dtype, o.is_contiguous(), o.stride(-1)))
+        r.zero_()
+
+    wide = torch.zeros(6, 8, dtype=torch.complex64)
+    W.run(P, wide[:, :5], launch, (2, 5))                 # a row stride: handed on as it is
+    W.run(P, wide.t()[:5], launch, (2, 6))                # column-major: copied
+    W.run(P, wide[0, ::2], launch, (2,))                  # strided vector: copied
+    assert seen == [(torch.complex64, False, 1), (torch.complex64, True, 1), (torch.complex64, True, 1)]
 
 
 # ---- against outputs of the reference's own base paths (tests/golden/wide_*.npz) ----------------------------------
@@ -96,15 +108,15 @@ def load_wide_golden(tag):
 
 
 @pytest.mark.parametrize("tag", sorted(GOLDEN_DTYPES))
-def test_arithmetic_against_reference_outputs(tag):
+def test_arithmetic_against_reference_outputs(tag, fsb_lib):
     g, dt = load_wide_golden(tag)
-    kind, reals = W.split_values(g["data"])
-    parts = [sp.csr_matrix((r.numpy(), g["indices"], g["indptr"]), shape=g["shape"]) for r in reals]
     wide = torch.complex128 if dt in W.COMPLEX_DTYPES else torch.float64
     a = sp.csr_matrix((g["data"].to(wide).numpy(), g["indices"], g["indptr"]), shape=g["shape"])
-    for operand, ref_out in ((g["x"], g["y"]), (g["B"], g["C"])):
-        out_shape = (g["shape"][0],) + tuple(operand.shape[1:])
-        got = W.product(kind, parts, operand, _launch, out_shape, dt)
+    ti, tp = torch.from_numpy(g["indices"]), torch.from_numpy(g["indptr"])
+    with fake_cuda():
+        got_y = fs.flagsparse_spmv_csr(g["data"], ti, tp, g["x"], g["shape"])
+        got_c = fs.flagsparse_spmm_csr(g["data"], ti, tp.to(torch.int64), g["B"], g["shape"])
+    for operand, ref_out, got in ((g["x"], g["y"], got_y), (g["B"], g["C"], got_c)):
         mag = np.asarray(abs(a) @ np.abs(operand.to(wide).numpy()))
         err = np.abs(got.to(wide).numpy() - ref_out.to(wide).numpy())
         assert got.dtype == ref_out.dtype and got.shape == ref_out.shape

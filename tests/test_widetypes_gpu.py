@@ -37,7 +37,9 @@ def _check(y, vals, i, p, shape, operand, dtype, what):
     ref, mag = np.asarray(a @ o), np.asarray(abs(a) @ np.abs(o))
     got = y.cpu().to(wide).numpy()
     assert y.dtype == dtype and got.shape == ref.shape, what
-    ratio = float((np.abs(got - ref) / np.maximum(mag, 1e-300)).max()) if ref.size else 0.0
+    # float16 results below 2^-14 are subnormal: their rounding error is absolute (half a step of 2^-24), not relative
+    floor = 2.0 ** -25 if dtype == torch.float16 else 0.0
+    ratio = float((np.maximum(np.abs(got - ref) - floor, 0) / np.maximum(mag, 1e-300)).max()) if ref.size else 0.0
     assert ratio <= TOL[dtype], f"{what}: {ratio:.3e}"
     assert not got[np.diff(p) == 0].any(), what
 
@@ -52,6 +54,35 @@ def _lens(kind):
 
 
 @pytest.mark.parametrize("dtype", W.WIDE_DTYPES, ids=str)
+@pytest.mark.parametrize("ptr_dtype", [torch.int32, torch.int64], ids=str)
+def test_direct_c_abi_call(cuda, fsb_lib, dtype, ptr_dtype):
+    """fsb_spmv_csr_wide itself: 2-byte values with float32 x / y, complex values interleaved."""
+    from flagsparse_b200 import _lib
+
+    lens = [0, 1, 0, 33, 2, 700, 0, 0, 5, 64, 31, 17] * 50
+    vals, i, p, shape = _case(dtype, lens, 900, seed=11)
+    x = _values(shape[1], dtype, 12)
+    half = dtype in W.HALF_DTYPES
+    dense = torch.float32 if half else dtype
+    d, ti, tp = vals.to(cuda), torch.from_numpy(i).to(cuda), torch.from_numpy(p).to(cuda).to(ptr_dtype)
+    tx = x.to(dense).to(cuda)
+    y = torch.full((shape[0],), 7, dtype=dense, device=cuda)
+    vt = {torch.float16: _lib.FSB_F16, torch.bfloat16: _lib.FSB_BF16, torch.complex64: _lib.FSB_C64,
+          torch.complex128: _lib.FSB_C128}[dtype]
+    st = torch.cuda.current_stream().cuda_stream
+    call = lambda out: fsb_lib.fsb_spmv_csr_wide(vt, 0 if ptr_dtype == torch.int32 else 1, d.data_ptr(), ti.data_ptr(),  # noqa: E731
+                                                 tp.data_ptr(), tx.data_ptr(), out.data_ptr(), shape[0], shape[1],
+                                                 d.numel(), st)
+    assert call(y) == 0
+    _check(y.to(dtype), vals, i, p, shape, x, dtype, "C ABI")
+    y2 = torch.empty_like(y)
+    assert call(y2) == 0 and torch.equal(y, y2)                       # fixed summation order
+    assert fsb_lib.fsb_spmv_csr_wide(0, 0, d.data_ptr(), ti.data_ptr(), tp.data_ptr(), tx.data_ptr(), y.data_ptr(),
+                                     shape[0], shape[1], d.numel(), st) == -1     # float32 is not this entry's
+    assert fsb_lib.fsb_spmv_csr_wide(vt, 0, None, None, tp.data_ptr(), None, None, 0, 5, 0, st) == 0   # no rows
+
+
+@pytest.mark.parametrize("dtype", W.WIDE_DTYPES, ids=str)
 @pytest.mark.parametrize("rows", ["uniform", "skewed"])
 def test_spmv(cuda, fsb_lib, dtype, rows):
     vals, i, p, shape = _case(dtype, _lens(rows), 12000, seed=3)
@@ -62,9 +93,7 @@ def test_spmv(cuda, fsb_lib, dtype, rows):
     assert torch.equal(fs.flagsparse_spmv_csr(d, ti, tp, tx, shape, use_opt=True), y)   # same kernels either way
     prep = fs.prepare_spmv_csr(d, ti, tp, shape)
     assert prep.data.dtype == dtype and not prep.supports_opt and prep.shape == shape
-    kind, parts = prep.wide
-    assert len(parts) == (1 if dtype in W.HALF_DTYPES else 2)
-    assert all(q.data.dtype == W.compute_dtype(dtype) and q.wide is None for q in parts)
+    assert prep.wide == ("native", [])          # read as stored by fsb_spmv_csr_wide: no widened or split copy
     y2, ms = fs.flagsparse_spmv_csr(x=tx, prepared=prep, return_time=True)
     _check(y2, vals, i, p, shape, x, dtype, "prepared")
     assert ms >= 0 and torch.equal(y2, fs.flagsparse_spmv_csr(x=tx, prepared=prep))
@@ -90,12 +119,18 @@ def test_spmm(cuda, fsb_lib, dtype):
     out = torch.empty_like(C)
     C2, ms = fs.flagsparse_spmm_csr(d, ti, tp, tB, shape, out=out, return_time=True)
     assert C2 is out and torch.equal(C2, C) and ms >= 0
-    # strided B
+    # column-major B (copied by the entry point) and B with a row stride (handed to the kernel as it is)
     Bt = tB.t().contiguous().t()
     assert torch.equal(fs.flagsparse_spmm_csr(d, ti, tp, Bt, shape), C)
+    wide = torch.zeros((shape[1], 11), dtype=dtype, device=cuda)
+    wide[:, 2:10] = tB
+    assert torch.equal(fs.flagsparse_spmm_csr(d, ti, tp, wide[:, 2:10], shape), C)
+    # wider than one column tile of the kernel
+    B40 = _values(shape[1] * 40, dtype, 23).reshape(shape[1], 40)
+    _check(fs.flagsparse_spmm_csr(d, ti, tp, B40.to(cuda), shape), vals, i, p, shape, B40, dtype, "spmm N=40")
     # the prepared ("opt") entry point is float32 / float64 only, as in the reference
     prep = fs.prepare_spmm_csr_opt(d, ti, tp, shape)
-    assert not prep.supports_opt and prep.data.dtype == dtype
+    assert not prep.supports_opt and prep.data.dtype == dtype and prep.wide == ("native", [])
     with pytest.raises(TypeError):
         fs.flagsparse_spmm_csr_opt(B=tB, prepared=prep)
     # COO entry point: same matrix given as unsorted triples
