@@ -391,6 +391,62 @@ def timed_pipeline(torch, api_call, host_in, host_out, steps, depth=2):
     return start.elapsed_time(end) / 1e3
 
 
+def timed_pipeline_sharded(torch, dist, run, host_in, host_out, dev_full, n_in, r0, r1, steps, barrier, lag):
+    """Sharded end-to-end steps with the stages of consecutive steps overlapped: the upload of this rank's 1/N of
+    the dense operand for step k+1 (its own stream, two device buffers) runs under the all-gather and the product of
+    step k (current stream), and the read-back of this rank's rows of step k (a third stream) under step k+1.
+    `lag`: how many products later the result buffer of a product is written again (the read-back of step k must be
+    over before product k+lag starts).  Every step still moves its own input and its own result inside the timed
+    region.  Returns seconds."""
+    dev = torch.cuda.current_device()
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream()
+    slices = [torch.empty(host_in.shape, dtype=host_in.dtype, device="cuda") for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]      # slice b is on the device
+    ev_used = [torch.cuda.Event() for _ in range(2)]    # slice b has been gathered
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def go(n):
+        reads = []
+        for k in range(n):
+            b = k % 2
+            with torch.cuda.stream(s_in):
+                if k >= 2:
+                    s_in.wait_event(ev_used[b])
+                slices[b].copy_(host_in, non_blocking=True)
+                ev_in[b].record(s_in)
+            main.wait_event(ev_in[b])
+            dist.all_gather_into_tensor(dev_full, slices[b])
+            ev_used[b].record(main)
+            if k >= lag:
+                main.wait_event(reads[k - lag])
+            res = run(dev_full[:n_in])
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                host_out.copy_(res[r0:r1], non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(s_out)
+                reads.append(e)
+        for st in (s_in, s_out):
+            fin = torch.cuda.Event()
+            fin.record(st)
+            main.wait_event(fin)
+
+    go(4)   # warm-up of the pipeline
+    barrier()
+    torch.cuda.synchronize()
+    start.record(main)
+    s_in.wait_event(start)
+    s_out.wait_event(start)
+    go(steps)
+    end.record(main)
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(end) / 1e3
+
+
 def event_time_ms(torch, fn, warm, iters):
     """Median over `iters` single calls, CUDA events around each (the protocol of the reference's own scripts)."""
     for _ in range(warm):
@@ -787,7 +843,9 @@ def run_sharded(args, workload, torch, device, rank, world):
 
     for _ in range(3):
         e2e_step()
-    e2e_elapsed = timed_region(torch, e2e_step, steps, barrier)
+    e2e_serial = timed_region(torch, e2e_step, steps, barrier)
+    lag = 2 if op.mode in ("peer", "fused") else 1
+    e2e_piped = timed_pipeline_sharded(torch, dist, run, host_in, host_out, dev_full, n_in, r0, r1, steps, barrier, lag)
 
     # parity: rank 0's assembled result against host-regenerated blocks; every rank's result against rank 0's
     res = run(dense).clone()
@@ -797,9 +855,10 @@ def run_sharded(args, workload, torch, device, rank, world):
     same = torch.tensor([1 if torch.equal(theirs, res) else 0], dtype=torch.int32, device=device)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     del theirs
-    t = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=device)
+    t = torch.tensor([elapsed, e2e_serial, e2e_piped], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed = float(t[0]), float(t[1])
+    elapsed, e2e_serial, e2e_piped = float(t[0]), float(t[1]), float(t[2])
+    e2e_elapsed = min(e2e_serial, e2e_piped)
     per_step = elapsed / steps
     value = nbytes / per_step / 1e9
     peak, peak_kind = measured_peak()
@@ -821,9 +880,11 @@ def run_sharded(args, workload, torch, device, rank, world):
             "e2e": {"value": nbytes / (e2e_elapsed / steps) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": host_in.numel() * host_in.element_size() * world,
                     "d2h_bytes_per_step": spec.n_rows * width * dense.element_size(),
-                    "ms_per_step": e2e_elapsed / steps * 1e3,
+                    "ms_per_step": e2e_elapsed / steps * 1e3, "serial_ms_per_step": e2e_serial / steps * 1e3,
                     "how": "each rank uploads 1/N of the dense operand, NCCL all-gather, product with the exchange, "
-                           "each rank reads back its own rows"},
+                           "each rank reads back its own rows"
+                           + ("; upload, product and read-back of consecutive steps overlapped on three streams"
+                              if e2e_piped < e2e_serial else "; one after the other")},
             "gpu_launches": launches * steps,
             "clocks": clocks.summary(),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
