@@ -11,7 +11,8 @@
  *   - Every pointer is a DEVICE pointer unless the comment says "host".
  *   - vtype: value dtype of data / x / B / y / C.  itype: dtype of `indices`.  ptype: dtype of `indptr`.
  *   - All work is enqueued on `stream` (a cudaStream_t passed as void*); no call synchronises the host
- *     and no call allocates or frees device memory -- the caller owns every buffer, scratch included.
+ *     and no call allocates or frees device memory -- the caller owns every buffer, scratch included (the one
+ *     exception is fsb_spmv_csr_noalloc, whose scratch is an array built into the library).
  *   - Return value: 0 on success, a negative FSB_E* code for an argument error detected on the host, or
  *     FSB_CUDA_ERROR_BASE + cudaError_t when a launch failed.
  *   - Inputs are assumed validated (indptr non-decreasing, indptr[0]==0, indptr[n_rows]==nnz,
