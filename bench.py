@@ -169,8 +169,8 @@ def cpu_sample(workload, rows_log2=None):
         return spec, rows, (d, i, p), dense, f"rows [0, {rows}) of {spec.n_rows}, B full"
     cfg, vdt, idt, pdt = SPMV_WORKLOADS[workload]
     spec = S.config_spec(cfg)
-    # c5: 1/32 of the rows (67 M entries, 0.5 GB of A) -- generating more on the host would take minutes
-    rows = min(spec.n_rows, 1 << (rows_log2 or (21 if workload == "c5" else 19)))
+    # c5: 1/16 of the rows (134 M entries, 1.1 GB of A; about a minute of generation on the host)
+    rows = min(spec.n_rows, 1 << (rows_log2 or (22 if workload == "c5" else 19)))
     r0 = 0 if spec.columns[0] != "band" else (spec.n_rows - rows) // 2
     d, i, p = S.generate_csr(spec, None, value_dtype=vdt, index_dtype=idt, indptr_dtype=pdt, row_range=(r0, r0 + rows))
     dense = S.dense_vector(spec, spec.n_cols, value_dtype=vdt)
