@@ -791,6 +791,9 @@ def run_sharded(args, workload, torch, device, rank, world):
         if op._slices is not None and op.prepared.algo == _lib.FSB_SPMV_PANEL:
             launches = len(op._slices)
             extra["slices"] = [e - b for b, e, _, _ in op._slices]
+        elif getattr(op, "_nccl_chunks", None) is not None:
+            launches = sum(1 for b, e in op._nccl_blocks if e > b)
+            extra["slices"] = [e - b for b, e in op._nccl_blocks]
         extra["kernel"] = op.prepared.opt_buckets[0]["kind"]
         if op.prepared.panel is not None:
             lay = op.prepared.panel

@@ -200,10 +200,13 @@ class ShardedCsrSpmv(_ShardedBase):
         self.mode = mode
         self._y = None
         self._slices = None
+        self._nccl_chunks = None
         if mode in ("peer", "fused"):
             self._setup_symmetric(1)
         if mode == "peer":
             self._plan_slices()
+        if mode == "nccl" and local_spmv is None and dist.is_initialized() and dist.get_backend(group) == "nccl":
+            self._plan_nccl_chunks()
 
     def _plan_slices(self):
         """Row slices of this shard, one launch each.  Only the panel kernel can be launched on a sub-range of its
@@ -237,9 +240,70 @@ class ShardedCsrSpmv(_ShardedBase):
         if self._y is None:
             self._y = torch.empty(self.n_rows, dtype=self.dtype, device=self.device)
         y = self._y
+        if self._nccl_chunks is not None:
+            return self._matvec_nccl_chunks(x, y)
         s, n = self.row_ranges[self.rank]
         self._local_into(x, y[s:s + n])
         self._all_gather_rows(y)
+        return y
+
+    def _plan_nccl_chunks(self):
+        """Mode "nccl" on a panel layout: the shard is computed in the same slices of row blocks as in mode "peer",
+        and slice j of every rank is gathered (on a stream of its own) while slice j+1 is computed.  Every rank needs
+        every rank's slice boundaries, and all ranks must issue the same number of collectives: the tables are
+        exchanged once, shorter ones padded with empty slices."""
+        self._nccl_chunks = None
+        p = self.prepared
+        if self.world == 1 or p is None or not self.device.type == "cuda":
+            return
+        mine = []
+        if p.algo == _lib.FSB_SPMV_PANEL and p.panel is not None and self.n_local > 0:
+            la = p.panel
+            sms = int(os.environ.get("FSB_SHARD_WAVE_BLOCKS", "0")) or \
+                torch.cuda.get_device_properties(self.device).multi_processor_count
+            mine = [(b, e, self.row_start + b * la.rb_rows, self.row_start + min(self.n_local, e * la.rb_rows))
+                    for b, e in slice_plan(la.n_row_blocks, sms, _max_slices())]
+        tables = [None] * self.world
+        dist.all_gather_object(tables, mine, group=self.group)
+        if any(len(t) == 0 for t in tables) or max(len(t) for t in tables) < 2:
+            return                       # some shard has no panel layout, or nothing to overlap
+        k = max(len(t) for t in tables)
+        rows = []
+        for r, t in enumerate(tables):
+            end = self.row_ranges[r][0] + self.row_ranges[r][1]
+            rows.append([(g0, g1) for _, _, g0, g1 in t] + [(end, end)] * (k - len(t)))
+        self._nccl_chunks = [[rows[r][j] for r in range(self.world)] for j in range(k)]
+        self._nccl_blocks = [(b, e) for b, e, _, _ in mine] + [(0, 0)] * (k - len(mine))
+        self._side = torch.cuda.Stream(self.device)
+
+    def _matvec_nccl_chunks(self, x, y):
+        from . import panel
+        from .spmv_csr import _validate_spmv_x
+
+        p = self.prepared
+        x = _validate_spmv_x(x, p)
+        main = torch.cuda.current_stream(self.device)
+        y_local = y[self.row_start: self.row_start + self.n_local]
+        for (b0, b1), ranges in zip(self._nccl_blocks, self._nccl_chunks):
+            if b1 > b0:
+                with torch.cuda.device(self.device):
+                    panel.launch_panel(p.panel, x, y_local, p.n_rows, p.n_cols, main.cuda_stream, b0, b1)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(ev)
+                views = [y[g0:g1] for g0, g1 in ranges]
+                sizes = {v.numel() for v in views}
+                if len(sizes) == 1 and views[0].numel() > 0:
+                    dist.all_gather(views, views[self.rank], group=self.group)
+                else:
+                    for r, v in enumerate(views):
+                        if v.numel() > 0:
+                            src = dist.get_global_rank(self.group, r) if self.group is not None else r
+                            dist.broadcast(v, src=src, group=self.group)
+        done = torch.cuda.Event()
+        done.record(self._side)
+        main.wait_event(done)
         return y
 
     def _matvec_peer(self, x):
