@@ -41,9 +41,16 @@ sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the step's dominant kernel, from the ncu captures
-# summarised under profiles/, each tied to the kernel source it was taken on: workload -> (bytes, source file,
-# first 12 hex digits of the file's sha256).  A capture of other sources is not reported (traffic: null).
-NCU_TRAFFIC_BYTES = {}
+# summarised under profiles/, each tied to the sources it was taken on: workload -> (bytes, source files relative to
+# the repository root, first 12 hex digits of the sha256 of their concatenation).  A capture of other sources is not
+# reported (traffic: null).  c5: the capture is of the same matrix law at 2^22 rows (1/16 of the rows, of the units
+# and of the entries), scaled by 16.
+_PANEL_SOURCES = ("flagsparse_b200/csrc/spmv_panel.cu", "flagsparse_b200/panel.py")
+NCU_TRAFFIC_BYTES = {
+    "c2": (1_098_600_000 + 3_455_744, _PANEL_SOURCES, "0f3f5cd4bcae"),        # profiles/spmv_panel_c2_f32.md
+    "c2f64": (1_673_750_000 + 3_496_960, _PANEL_SOURCES, "0f3f5cd4bcae"),     # profiles/spmv_panel_c2_f64.md
+    "c5": (16 * (1_122_595_000 + 3_258_624), _PANEL_SOURCES, "0f3f5cd4bcae"),  # profiles/spmv_panel_c5like_f32.md
+}
 
 SPMV_WORKLOADS = {
     "c1": ("c1", "float32", "int32", "int32"),
@@ -80,12 +87,15 @@ def measured_traffic(workload):
     entry = NCU_TRAFFIC_BYTES.get(workload)
     if entry is None:
         return None
-    nbytes, source, sha = entry
+    nbytes, sources, sha = entry
+    h = hashlib.sha256()
     try:
-        with open(os.path.join(ROOT, "flagsparse_b200", "csrc", source), "rb") as f:
-            return nbytes if hashlib.sha256(f.read()).hexdigest()[:12] == sha else None
+        for source in sources:
+            with open(os.path.join(ROOT, source), "rb") as f:
+                h.update(f.read())
     except OSError:
         return None
+    return nbytes if h.hexdigest()[:12] == sha else None
 
 
 class ClockSampler:
