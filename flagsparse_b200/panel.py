@@ -242,6 +242,97 @@ def pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, 
     return val, rc, upiece, n_pieces, max_run, n_runs
 
 
+def pack_pieces_core(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, rounds, max_slot_overhead,
+                     n_buffers=2, pad_row=0xFFFF):
+    """pack_pieces for layouts in which most rows have ONE entry per unit (wide bands).  Such entries can sit in any
+    slot of any piece of their unit, so the bulk of a unit is laid out with lane l holding only entries whose
+    accumulator index is l modulo 32: the 32 accumulators of a round then lie in 32 different shared-memory banks
+    and their load and store take one pass each.  Per unit, the single entries of every class l are listed in row
+    order; with J = (shortest list) // rounds, the first J * rounds entries of every list fill J "core" pieces
+    completely (piece j takes entries j * rounds .. of every list, lane l from list l) -- no padding.  What is left
+    (the tails of the longer lists, and every row with several entries in the unit) is packed by pack_pieces as
+    before, into pieces that follow the core pieces of their unit.  Same return value as pack_pieces."""
+    dev = data_p.device
+    nnz = data_p.numel()
+    sv = data_p.element_size()
+    SLOTS = 32 * rounds
+    n_units = ustart.numel() - 1
+    fallback = lambda: pack_pieces(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_ord, CW, rounds,  # noqa: E731
+                                   max_slot_overhead, n_buffers=n_buffers, pad_row=pad_row)
+    ar = torch.arange(nnz, device=dev)
+    new_run = torch.ones(nnz, dtype=torch.bool, device=dev)
+    new_run[1:] = (run_key_p[1:] != run_key_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
+    run_id = torch.cumsum(new_run.to(torch.int64), 0) - 1
+    n_runs = int(run_id[-1].item()) + 1
+    if nnz >= RUNS_MIN_MEAN * n_runs:
+        return fallback()                       # rows with several entries per unit: the run-summing layout
+    run_first = ar[new_run]
+    run_len = torch.diff(run_first, append=torch.tensor([nnz], device=dev))
+    single = run_len[run_id] == 1
+    del new_run, run_id, run_first, run_len
+    idx_s = torch.nonzero(single, as_tuple=False).flatten()
+    del single
+    key_s = unit_of_entry[idx_s] * 32 + acc_p[idx_s] % 32
+    key_sorted, order = torch.sort(key_s, stable=True)          # row order survives inside a (unit, class) list
+    idx_sorted = idx_s[order]
+    del key_s, order, idx_s
+    cnt = torch.bincount(key_sorted, minlength=n_units * 32)
+    J = cnt.view(n_units, 32).min(dim=1).values // rounds       # core pieces of each unit
+    if int(J.sum().item()) * SLOTS * 4 < nnz:
+        return fallback()                       # too few entries would profit
+    rank = torch.arange(key_sorted.numel(), device=dev) - _cumsum0(cnt)[:-1][key_sorted]
+    unit_s = key_sorted // 32
+    in_core = rank < J[unit_s] * rounds
+    core_idx, core_rank = idx_sorted[in_core], rank[in_core]
+    core_unit, core_lane = unit_s[in_core], key_sorted[in_core] % 32
+    del rank, unit_s, in_core, idx_sorted, key_sorted, cnt
+    # the rest, unit by unit in the old order, through the ordinary packer (units without a rest are left out of it)
+    rest = torch.ones(nnz, dtype=torch.bool, device=dev)
+    rest[core_idx] = False
+    rest_idx = torch.nonzero(rest, as_tuple=False).flatten()
+    del rest
+    L = torch.zeros(n_units, dtype=torch.int64, device=dev)     # pieces of the rest, per unit
+    max_run, rest_pieces = 1, 0
+    if rest_idx.numel() > 0:
+        rcnt = torch.bincount(unit_of_entry[rest_idx], minlength=n_units)
+        has = rcnt > 0
+        compact = torch.cumsum(has.to(torch.int64), 0) - 1
+        packed = pack_pieces(data_p[rest_idx], acc_p[rest_idx], cols_p[rest_idx], run_key_p[rest_idx],
+                             compact[unit_of_entry[rest_idx]], _cumsum0(rcnt[has]), u_ord[has], CW, rounds, None,
+                             n_buffers=n_buffers, pad_row=pad_row)
+        if packed is None:
+            return None
+        r_val, r_rc, r_upiece, rest_pieces, max_run, _ = packed
+        L[has] = r_upiece[1:] - r_upiece[:-1]
+        has_units = torch.nonzero(has, as_tuple=False).flatten()
+    upiece = _cumsum0(J + L)
+    n_pieces = int(upiece[-1].item())
+    if max_slot_overhead is not None and n_pieces * SLOTS > max_slot_overhead * nnz + 4096:
+        return None
+    val = torch.zeros(n_pieces * SLOTS, dtype=data_p.dtype, device=dev)
+    rc = torch.full((n_pieces * SLOTS,), pad_row << 16, dtype=torch.int64, device=dev)
+    rc = torch.where(rc >= 2**31, rc - 2**32, rc).to(torch.int32)
+    # core entries: piece = j-th core piece of the unit, lane = class, round = position in the slice of the list
+    piece = upiece[core_unit] + core_rank // rounds
+    k_ = core_rank % rounds
+    E = 16 // sv
+    pos_val = piece * SLOTS + (k_ // E) * (32 * E) + core_lane * E + k_ % E
+    pos = piece * SLOTS + (k_ >> 2) * 128 + core_lane * 4 + (k_ & 3)
+    val[pos_val] = data_p[core_idx]
+    c = cols_p[core_idx]
+    word = (acc_p[core_idx] << 16) | ((u_ord[core_unit] % n_buffers) * CW + (c - (c // CW) * CW))
+    rc[pos] = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
+    del piece, k_, pos_val, pos, word, c
+    if rest_pieces > 0:
+        q = torch.arange(rest_pieces, device=dev)
+        cu = torch.searchsorted(r_upiece, q, right=True) - 1           # (compacted) unit of each piece of the rest
+        ru = has_units[cu]
+        newp = upiece[ru] + J[ru] + (q - r_upiece[cu])
+        val.view(n_pieces, SLOTS)[newp] = r_val.view(rest_pieces, SLOTS)
+        rc.view(n_pieces, SLOTS)[newp] = r_rc.view(rest_pieces, SLOTS)
+    return val, rc, upiece, n_pieces, max_run, n_runs
+
+
 def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slot_overhead):
     """The units and pieces of rows r0 .. r1-1 (whole row blocks).  Returns (val, rc, first piece of each unit + total,
     chunk of each unit, row block of each unit, number of pieces, longest run); () when the rows hold no entry;
@@ -271,8 +362,9 @@ def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slo
     n_b = -(-(r1 - r0) // RB)
     first_unit = torch.searchsorted(u_rb.contiguous(), torch.arange(b0, b0 + n_b, device=dev))
     u_ord = torch.arange(n_units, device=dev) - first_unit[u_rb - b0]
-    packed = pack_pieces(data[e0:e1][perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord,
-                         CW, rounds, max_slot_overhead, n_buffers=NB, pad_row=RB)
+    packer = pack_pieces if os.environ.get("FSB_PANEL_NO_CORE") else pack_pieces_core
+    packed = packer(data[e0:e1][perm], rows_p - (rows_p // RB) * RB, cols_p, rows_p, unit_of_entry, ustart, u_ord,
+                    CW, rounds, max_slot_overhead, n_buffers=NB, pad_row=RB)
     if packed is None:
         return None
     val, rc, upiece, n_pieces, max_run, n_runs = packed

@@ -195,3 +195,34 @@ def test_layout_with_more_x_buffers(fsb_lib, monkeypatch, n_buffers):
     assert seen == d.size
     ref, mag = O.spmv_f64(d, i, p, (spec.n_rows, spec.n_cols), x)
     assert O.max_bound_ratio(y, ref, mag) <= 1e-12
+
+
+def test_single_entry_rows_get_core_pieces(fsb_lib, monkeypatch):
+    """A wide band (about one entry per row and unit): most pieces are "core" pieces in which lane l holds only
+    accumulators congruent to l modulo 32, the rest follow them; the whole layout still evaluates to the product."""
+    spec = S.config_spec("c5").scaled(600000)           # band of +-300000 columns: 0.44 entries per row and chunk
+    d, i, p = (torch.from_numpy(a) for a in S.generate_csr(spec, None, indptr_dtype="int64"))
+    lay = panel.build_panel_layout(d, i, p, spec.n_rows, spec.n_cols, 70, force=True, rounds=8)
+    assert lay is not None and not (lay.flags & panel.FLAG_RUNS)
+    slots = fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds)
+    x = S.dense_vector(spec, spec.n_cols).astype(np.float64)
+    y, seen = _evaluate(lay, x, spec.n_rows, spec.n_cols, slots)
+    assert seen == d.numel()
+    ref, _ = O.spmv_f64(d.numpy(), i.numpy(), p.numpy(), (spec.n_rows, spec.n_cols), x)
+    assert np.allclose(y, ref, rtol=0, atol=1e-9)
+    # count the pieces whose every lane stays inside its own class
+    rc = lay.rc.numpy().astype(np.int64) & 0xFFFFFFFF
+    R = lay.rounds
+    core = full = 0
+    for pc in range(lay.n_pieces):
+        sl = np.arange(slots)
+        ln, k = sl // R, sl % R
+        rloc = rc[pc * slots + (k // 4) * 128 + ln * 4 + k % 4] >> 16
+        live = rloc != lay.pad_row
+        full += int(live.all())
+        core += int(live.all() and np.all(rloc % 32 == ln))
+    assert core > 0.3 * lay.n_pieces and core <= full, (core, full, lay.n_pieces)
+    # the same matrix without core pieces has the same number of entries in (a few) fewer, fuller pieces at most
+    monkeypatch.setenv("FSB_PANEL_NO_CORE", "1")
+    plain = panel.build_panel_layout(d, i, p, spec.n_rows, spec.n_cols, 70, force=True, rounds=8)
+    assert plain.n_units == lay.n_units and lay.n_pieces <= plain.n_pieces * 1.1
