@@ -49,7 +49,7 @@ _PANEL_SOURCES = ("flagsparse_b200/csrc/spmv_panel.cu", "flagsparse_b200/panel.p
 NCU_TRAFFIC_BYTES = {
     "c2": (1_098_600_000 + 3_455_744, _PANEL_SOURCES, "34216c4bb62e"),        # profiles/spmv_panel_c2_f32.md
     "c2f64": (1_673_750_000 + 3_496_960, _PANEL_SOURCES, "34216c4bb62e"),     # profiles/spmv_panel_c2_f64.md
-    "c5": (16 * (1_122_595_000 + 3_258_624), _PANEL_SOURCES, "34216c4bb62e"),  # profiles/spmv_panel_c5like_f32.md
+    "c5": (16 * (1_122_492_000 + 3_389_696), _PANEL_SOURCES, "34216c4bb62e"),  # profiles/spmv_panel_c5like_f32.md
 }
 
 SPMV_WORKLOADS = {
