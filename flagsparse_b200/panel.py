@@ -264,8 +264,10 @@ def pack_pieces_core(data_p, acc_p, cols_p, run_key_p, unit_of_entry, ustart, u_
     new_run[1:] = (run_key_p[1:] != run_key_p[:-1]) | (unit_of_entry[1:] != unit_of_entry[:-1])
     run_id = torch.cumsum(new_run.to(torch.int64), 0) - 1
     n_runs = int(run_id[-1].item()) + 1
-    if nnz >= RUNS_MIN_MEAN * n_runs:
-        return fallback()                       # rows with several entries per unit: the run-summing layout
+    if nnz >= RUNS_MIN_MEAN * n_runs or sv != 4:
+        # rows with several entries per unit keep the run-summing layout; 8-byte accumulators span two banks each,
+        # so 32 lanes cannot all have a bank of their own
+        return fallback()
     run_first = ar[new_run]
     run_len = torch.diff(run_first, append=torch.tensor([nnz], device=dev))
     single = run_len[run_id] == 1
