@@ -346,29 +346,66 @@ spmv_stream_kernel(const V* __restrict__ data, const I* __restrict__ idx, const 
   }
 }
 
-// one thread per tile t >= 1: if the first row written by tile t started in an earlier tile, finish it
+// Neumaier-compensated running sum in double: exact enough for either value type whatever the row length
+__device__ __forceinline__ void comp_add(double& sum, double& comp, double v) {
+  const double s2 = sum + v;
+  comp += (fabs(sum) >= fabs(v)) ? ((sum - s2) + v) : ((v - s2) + sum);
+  sum = s2;
+}
+
+constexpr int kFixupSerial = 32;   // a row that crossed more tiles than this is summed by its whole warp
+
+// one thread per tile t >= 1: if the first row written by tile t started in an earlier tile, finish it.
+// The carries of a row that crossed many tiles (a single row of 2^30 entries leaves half a million of them) are
+// summed by the 32 lanes of the thread's warp, lane-strided, and combined in a fixed order.
 template <typename V, typename P, typename Out>
 __global__ void __launch_bounds__(kThreads)
 spmv_fixup_kernel(const P* __restrict__ ptr, const int32_t* __restrict__ tile_row,
                   const V* __restrict__ carry, const V* __restrict__ head, Out out, int64_t n_tiles,
                   int log2_tile) {
   const int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x + 1;
-  if (t >= n_tiles) return;
-  const int32_t ra = tile_row[t];
-  const int32_t rb = tile_row[t + 1];
-  if (ra >= rb) return;                       // no row ends in this tile
-  const int64_t p = (int64_t)ptr[ra];
-  if (p >= (t << log2_tile)) return;          // its first row starts inside the tile
-  const int64_t t0 = p >> log2_tile;
-  // Neumaier-compensated sum in double: exact enough for either value type whatever the row length
-  double sum = (double)head[t], comp = 0.0;
-  for (int64_t u = t0; u < t; ++u) {
-    const double v = (double)carry[u];
-    const double s2 = sum + v;
-    comp += (fabs(sum) >= fabs(v)) ? ((sum - s2) + v) : ((v - s2) + sum);
-    sum = s2;
+  const int lane = threadIdx.x & 31;
+  int32_t ra = 0;
+  long long t0 = 0;
+  bool need = false;
+  if (t < n_tiles) {
+    ra = tile_row[t];
+    if (ra < tile_row[t + 1]) {                 // some row ends in this tile
+      const int64_t p = (int64_t)ptr[ra];
+      if (p < (t << log2_tile)) {               // and its first row started in an earlier one
+        need = true;
+        t0 = p >> log2_tile;
+      }
+    }
   }
-  out.store((int64_t)ra, (V)(sum + comp));
+  const bool wide = need && ((long long)t - t0) > kFixupSerial;
+  if (need && !wide) {
+    double sum = (double)head[t], comp = 0.0;
+    for (int64_t u = t0; u < t; ++u) comp_add(sum, comp, (double)carry[u]);
+    out.store((int64_t)ra, (V)(sum + comp));
+  }
+  unsigned todo = __ballot_sync(0xffffffffu, wide);
+  while (todo) {
+    const int src = __ffs(todo) - 1;
+    todo &= todo - 1;
+    const long long a = __shfl_sync(0xffffffffu, t0, src);
+    const long long b = __shfl_sync(0xffffffffu, (long long)t, src);
+    double sum = 0.0, comp = 0.0;
+    for (long long u = a + lane; u < b; u += 32) comp_add(sum, comp, (double)carry[u]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const double os = __shfl_down_sync(0xffffffffu, sum, o);
+      const double oc = __shfl_down_sync(0xffffffffu, comp, o);
+      comp_add(sum, comp, os);
+      comp += oc;
+    }
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    comp = __shfl_sync(0xffffffffu, comp, 0);
+    if (lane == src) {
+      comp_add(sum, comp, (double)head[t]);
+      out.store((int64_t)ra, (V)(sum + comp));
+    }
+  }
 }
 
 template <typename V, typename Out>

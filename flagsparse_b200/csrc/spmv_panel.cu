@@ -487,7 +487,7 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
   if (n_rows < 0 || n_cols < 0 || n_row_blocks < 0 || rb_rows <= 0 || rb_rows >= 65535) return FSB_EINVAL;
-  if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
+  if (chunk_cols <= 0 || (chunk_cols % 4) != 0 || chunk_cols > 16384) return FSB_EINVAL;
   if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
   if (fsb_spmv_panel_piece_slots(rounds) == 0) return FSB_EINVAL;
   if (block_begin < 0 || block_end > n_row_blocks || block_begin > block_end) return FSB_EINVAL;
@@ -530,7 +530,7 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
   if (n_cols < 0 || n_ctas < 0 || n_long < 0 || max_group_acc < 0 || max_group_acc >= 65535) return FSB_EINVAL;
-  if (chunk_cols <= 0 || (chunk_cols & (chunk_cols - 1)) != 0 || chunk_cols > 16384) return FSB_EINVAL;
+  if (chunk_cols <= 0 || (chunk_cols % 4) != 0 || chunk_cols > 16384) return FSB_EINVAL;
   if (!panel_buffers_ok(n_buffers, chunk_cols)) return FSB_EINVAL;
   if (fsb_spmv_panel_piece_slots(rounds) == 0) return FSB_EINVAL;
   if (n_long == 0 || n_ctas == 0) return FSB_OK;

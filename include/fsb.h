@@ -136,6 +136,8 @@ int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void* data, cons
  *   val[s], rc[s]        per slot: value and packed word (local row << 16 | buffer * chunk_cols + local
  *                        column), buffer = ordinal of the unit inside its row block modulo n_buffers; unused
  *                        slots carry value 0, column 0 and local row = rb_rows (a spare accumulator)
+ *   chunk_cols           columns of x per unit: a multiple of 4, at most 16384 (a chunk is one bulk copy into
+ *                        shared memory; the host code uses 10240 for float32 and 4096 for float64)
  *   rounds               4, 8 or 16: slots per lane and piece.  Small pieces suit units with few entries
  *                        (every warp of the CTA gets work in every unit)
  *   flags                FSB_PANEL_RUNS: rows have several entries per unit on average; the kernel then sums a

@@ -188,7 +188,7 @@ def test_layout_with_more_x_buffers(fsb_lib, monkeypatch, n_buffers):
     lay = panel.build_panel_layout(torch.from_numpy(d), torch.from_numpy(i), torch.from_numpy(p), spec.n_rows,
                                    spec.n_cols, int(np.diff(p).max()), force=True)
     if n_buffers == 8:
-        assert lay is None          # eight float32 chunks of 8192 columns leave no room for the accumulators
+        assert lay is None          # eight float32 chunks of 10240 columns leave no room for the accumulators
         return
     assert lay.n_buffers == n_buffers
     y, seen = _evaluate(lay, x.astype(np.float64), spec.n_rows, spec.n_cols, fsb_lib.fsb_spmv_panel_piece_slots(lay.rounds))

@@ -128,6 +128,21 @@ def test_stream_tunings_stay_in_tolerance(cuda, fsb_lib, tuning):
     assert_spmv_ok(y, data, idx, ptr, (len(lens), 8192), x, what=f"mixed tuning {tuning}")
 
 
+@pytest.mark.parametrize("tuning", STREAM_TUNINGS)
+@pytest.mark.parametrize("vdt", [np.float32, np.float64])
+def test_stream_rows_across_many_tiles(cuda, fsb_lib, tuning, vdt):
+    """Rows that cross hundreds of tiles: their carries are summed by a whole warp of the fix-up kernel, the
+    shorter crossings beside them by one thread each."""
+    lens = [3, 700_000, 0, 5000, 1, 150_000, 40_000, 2, 300_001, 7]
+    n_cols = 1 << 20
+    data, idx, ptr = handmade_csr(21, lens, n_cols, value_dtype=vdt)
+    x = np.random.default_rng(22).uniform(-1, 1, n_cols).astype(vdt)
+    y = spmv(data, idx, ptr, (len(lens), n_cols), x, algo="stream", tuning=tuning)
+    assert_spmv_ok(y, data, idx, ptr, (len(lens), n_cols), x, what=f"rows across many tiles, tuning {tuning}")
+    y2 = spmv(data, idx, ptr, (len(lens), n_cols), x, algo="stream", tuning=tuning)
+    assert np.array_equal(y, y2)
+
+
 @pytest.mark.parametrize("lanes", [2, 4, 8, 16, 32])
 def test_vector_lane_counts(cuda, fsb_lib, lanes):
     spec = S.config_spec("c2").scaled(5000)
