@@ -9,7 +9,10 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libfsb.so")
+# FSB_BOUNDS_CHECK=1 in the environment selects the checking build (python -m flagsparse_b200.build --check): every
+# product entry point then walks its index arrays first and refuses, with a record, a call that would leave them
+CHECKING = os.environ.get("FSB_BOUNDS_CHECK", "") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "csrc", "libfsb_check.so" if CHECKING else "libfsb.so")
 
 FSB_F32, FSB_F64 = 0, 1
 FSB_F16, FSB_BF16, FSB_C64, FSB_C128 = 2, 3, 4, 5     # fsb_spmv_csr_wide only
@@ -26,6 +29,18 @@ _ERRORS = {
     -3: "FSB_EALIGN (pointer not aligned to its element size)",
     -4: "FSB_ESCRATCH (scratch buffer too small)",
     -5: "FSB_ENOSPACE (matrix too large for the built-in scratch array)",
+    -6: "FSB_EBOUNDS (checking build: an index array would take a kernel out of bounds; nothing was launched)",
+}
+FSB_EBOUNDS = -6
+BAD_KINDS = {
+    1: "column index outside [0, n_cols)",
+    2: "row pointer outside [0, nnz]",
+    3: "row pointer smaller than the one before it",
+    4: "row id outside [0, n_rows)",
+    5: "panel slot with an accumulator beyond the spare one",
+    6: "panel slot with an x position beyond the x buffers",
+    7: "unit with a column chunk beyond n_cols",
+    8: "unit or piece pointer table negative or decreasing",
 }
 
 _c = ctypes
@@ -62,6 +77,8 @@ SIGNATURES = {
     "fsb_spmm_csr_wide": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "fsb_sddmm_csr": (_i32, [_i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double,
                              _c.c_double, _vp]),
+    "fsb_bounds_check_enabled": (_i32, []),
+    "fsb_bounds_check_report": (_i32, [_vp]),
 }
 
 _lib = None
@@ -73,8 +90,8 @@ def lib():
     if _lib is None:
         if not os.path.exists(LIB_PATH):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python -m flagsparse_b200.build` "
-                "(this package has no fallback path)"
+                f"{LIB_PATH} is missing: build it with `python -m flagsparse_b200.build"
+                f"{' --check' if CHECKING else ''}` (this package has no fallback path)"
             )
         handle = ctypes.CDLL(LIB_PATH)
         for name, (restype, argtypes) in SIGNATURES.items():
@@ -91,4 +108,15 @@ def check(rc, what):
         return
     if rc >= FSB_CUDA_ERROR_BASE:
         raise RuntimeError(f"{what}: CUDA error {rc - FSB_CUDA_ERROR_BASE}")
+    if rc == FSB_EBOUNDS:
+        seen, kind, where, value, limit = bounds_report()
+        raise IndexError(f"{what}: {_ERRORS[rc]}: {BAD_KINDS.get(kind, kind)} at position {where} "
+                         f"(value {value}, limit {limit}; {seen} violation(s) seen)")
     raise RuntimeError(f"{what}: {_ERRORS.get(rc, rc)}")
+
+
+def bounds_report():
+    """(violations seen, kind, position, value, limit) of the last call the checking build refused; clears it."""
+    out = (ctypes.c_int64 * 5)()
+    lib().fsb_bounds_check_report(ctypes.cast(out, ctypes.c_void_p))
+    return tuple(int(v) for v in out)

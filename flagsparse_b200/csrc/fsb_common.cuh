@@ -18,6 +18,26 @@ inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? FSB_OK : FSB_CUDA_
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 __device__ __forceinline__ bool aligned_to_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// ---- the checking build: entry points walk their index arrays first (bounds_check.cu) ----------------
+#ifdef FSB_BOUNDS_CHECK
+int check_csr(int itype, int ptype, const void* indices, const void* indptr, int64_t n_rows, int64_t n_cols,
+              int64_t nnz, cudaStream_t st);
+int check_entry_ids(const int32_t* indices, const int32_t* row_ids, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                    cudaStream_t st);
+int check_panel(const uint32_t* rc_words, const int32_t* unit_piece_ptr, const int32_t* unit_chunk,
+                const int32_t* owner_unit_ptr, int n_owners, int slots, int max_row, int chunk_cols, int n_buffers,
+                int64_t n_cols, cudaStream_t st);
+#define FSB_WALK_FIRST(call)                       \
+  do {                                             \
+    const int rc__ = ::fsb::call;                  \
+    if (rc__ != FSB_OK) return rc__;               \
+  } while (0)
+#else
+#define FSB_WALK_FIRST(call) \
+  do {                       \
+  } while (0)
+#endif
+
 // ---- streaming (read-once) loads: evict-first so that A does not push x / B out of L2 -------------
 template <typename T>
 __device__ __forceinline__ T ld_stream(const T* p) {

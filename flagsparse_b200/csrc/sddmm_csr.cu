@@ -237,6 +237,7 @@ extern "C" int fsb_sddmm_csr(int vtype, const int32_t* indices, const int32_t* r
   if (!aligned_to(X, sv) || !aligned_to(Y, sv) || !aligned_to(out, sv) || !aligned_to(data, sv) ||
       !aligned_to(indices, 4) || !aligned_to(row_ids, 4))
     return FSB_EALIGN;
+  FSB_WALK_FIRST(check_entry_ids(indices, row_ids, n_rows, n_cols, nnz, st));
   if (vtype == FSB_F32)
     return sddmm_typed<float>(indices, row_ids, X, ldx, Y, ldy, data, out, nnz, (int)k_dim, alpha, beta, st);
   return sddmm_typed<double>(indices, row_ids, X, ldx, Y, ldy, data, out, nnz, (int)k_dim, alpha, beta, st);

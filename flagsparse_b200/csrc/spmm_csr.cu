@@ -327,6 +327,7 @@ extern "C" int fsb_spmm_csr(int vtype, int itype, int ptype, const void* data, c
   if (C == nullptr || indptr == nullptr || ldc < n_dense) return FSB_EINVAL;
   const size_t sv = vtype == FSB_F32 ? 4 : 8, si = itype == FSB_I32 ? 4 : 8, sp = ptype == FSB_I32 ? 4 : 8;
   if (!aligned_to(C, sv) || !aligned_to(indptr, sp)) return FSB_EALIGN;
+  FSB_WALK_FIRST(check_csr(itype, ptype, indices, indptr, n_rows, n_cols, nnz, st));
   if (nnz == 0 && accumulate) return FSB_OK;   // nothing to add
   if (nnz == 0) {
     const int64_t n = n_rows * n_dense;

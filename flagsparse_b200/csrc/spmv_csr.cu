@@ -586,6 +586,7 @@ extern "C" int fsb_spmv_csr(int vtype, int itype, int ptype, const void* data, c
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
   if (rc != FSB_OK) return rc;
+  FSB_WALK_FIRST(check_csr(itype, ptype, indices, indptr, n_rows, n_cols, nnz, st));
   if (n_rows == 0) return FSB_OK;
   if (y == nullptr) return FSB_EINVAL;
   const size_t sv = vtype == FSB_F32 ? 4 : 8;
@@ -612,6 +613,7 @@ extern "C" int fsb_spmv_csr_scatter(int vtype, int itype, int ptype, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
   if (rc != FSB_OK) return rc;
+  FSB_WALK_FIRST(check_csr(itype, ptype, indices, indptr, n_rows, n_cols, nnz, st));
   if (y_peers == nullptr || n_peers < 1 || n_peers > 64 || row_offset < 0) return FSB_EINVAL;
   if (first_peer < 0 || first_peer >= n_peers) return FSB_EINVAL;
   if (n_rows == 0) return FSB_OK;
@@ -683,6 +685,7 @@ extern "C" int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   int rc = check_common(vtype, itype, ptype, data, indices, indptr, x, n_rows, n_cols, nnz);
   if (rc != FSB_OK) return rc;
+  FSB_WALK_FIRST(check_csr(itype, ptype, indices, indptr, n_rows, n_cols, nnz, st));
   if (n_rows == 0) return FSB_OK;
   if (y == nullptr) return FSB_EINVAL;
   const size_t sv = vtype == FSB_F32 ? 4 : 8;

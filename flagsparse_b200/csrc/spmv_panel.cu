@@ -497,6 +497,8 @@ extern "C" int fsb_spmv_csr_panel(int vtype, const void* val, const uint32_t* rc
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, rb_rows, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
+  FSB_WALK_FIRST(check_panel(rc, unit_piece_ptr, unit_chunk, rb_unit_ptr, n_row_blocks,
+                             fsb_spmv_panel_piece_slots(rounds), rb_rows, chunk_cols, n_buffers, n_cols, st));
   const int mode = (flags & FSB_PANEL_LONG_RUNS) ? kModeRunsClash : ((flags & FSB_PANEL_RUNS) ? kModeRuns : kModeDirect);
   const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0, (uint32_t)rb_rows};
   const unsigned grid = (unsigned)(block_end - block_begin);
@@ -540,6 +542,8 @@ extern "C" int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint3
   const size_t smem = fsb_spmv_panel_smem_bytes(vtype, max_group_acc, chunk_cols, n_buffers);
   if (smem + sizeof(PanelStatic) > 227 * 1024) return FSB_ERANGE;
   if (!aligned_to(val, 16) || !aligned_to(rc, 16)) return FSB_EALIGN;
+  FSB_WALK_FIRST(check_panel(rc, unit_piece_ptr, unit_chunk, cta_unit_ptr, n_ctas, fsb_spmv_panel_piece_slots(rounds),
+                             max_group_acc, chunk_cols, n_buffers, n_cols, st));
   const int mode = (flags & FSB_PANEL_LONG_RUNS) ? kModeRunsClash : ((flags & FSB_PANEL_RUNS) ? kModeRuns : kModeDirect);
   const PanelGeom gm{n_cols, chunk_cols, n_buffers, (flags & FSB_PANEL_DEBUG_TIMEOUT) ? 1 : 0,
                      (uint32_t)max_group_acc};

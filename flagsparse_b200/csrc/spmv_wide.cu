@@ -168,6 +168,7 @@ extern "C" int fsb_spmv_csr_wide(int vtype, int ptype, const void* data, const i
   if (!aligned_to(data, sv) || !aligned_to(x, sd) || !aligned_to(y, sd) || !aligned_to(indices, 4) ||
       !aligned_to(indptr, ptype == FSB_I32 ? 4 : 8))
     return FSB_EALIGN;
+  FSB_WALK_FIRST(check_csr(FSB_I32, ptype, indices, indptr, n_rows, n_cols, nnz, st));
 #define FSB_WIDE_TYPE(S_)                                                                                     \
   return ptype == FSB_I32 ? wide_launch<S_, int32_t>(data, indices, indptr, x, y, n_rows, nnz, st)            \
                           : wide_launch<S_, int64_t>(data, indices, indptr, x, y, n_rows, nnz, st)
@@ -211,6 +212,7 @@ extern "C" int fsb_spmm_csr_wide(int vtype, int ptype, const void* data, const i
   if (!aligned_to(data, sv) || !aligned_to(B, sd) || !aligned_to(C, sd) || !aligned_to(indices, 4) ||
       !aligned_to(indptr, ptype == FSB_I32 ? 4 : 8))
     return FSB_EALIGN;
+  FSB_WALK_FIRST(check_csr(FSB_I32, ptype, indices, indptr, n_rows, n_cols, nnz, st));
 #define FSB_WIDE_TYPE(S_)                                                                                         \
   return ptype == FSB_I32                                                                                         \
              ? wide_spmm_launch<S_, int32_t>(data, indices, indptr, B, ldb, C, ldc, n_rows, (int)n_dense, st)      \

@@ -48,6 +48,7 @@ extern "C" {
 #define FSB_EALIGN (-3)      /* pointer not aligned to its element size                      */
 #define FSB_ESCRATCH (-4)    /* scratch buffer smaller than fsb_*_scratch_bytes() asks for   */
 #define FSB_ENOSPACE (-5)    /* problem too large for the library's built-in scratch array   */
+#define FSB_EBOUNDS (-6)     /* checking build only: an index array would take a kernel out of bounds; nothing ran */
 #define FSB_CUDA_ERROR_BASE 1000
 
 /* SpMV algorithm selector */
@@ -278,6 +279,28 @@ int fsb_spmm_csr_wide(int vtype, int ptype, const void* data, const int32_t* ind
 int fsb_sddmm_csr(int vtype, const int32_t* indices, const int32_t* row_ids, const void* X, int64_t ldx,
                   const void* Y, int64_t ldy, const void* data, void* out, int64_t n_rows, int64_t n_cols,
                   int64_t nnz, int64_t k_dim, double alpha, double beta, void* stream);
+
+/*
+ * The checking build (the same sources compiled with -DFSB_BOUNDS_CHECK into libfsb_check.so; the stand-in for a
+ * memory checker on hosts where none can be run).  There every product entry point above first walks the index arrays
+ * it was handed -- column indices against n_cols, row pointers against nnz and against each other, SDDMM row ids
+ * against n_rows, the packed words and unit tables of a panel layout against the shared-memory arrays they index --
+ * waits for the walk, and if anything is out of range returns FSB_EBOUNDS without launching the product: no trap, no
+ * fault, the context stays usable.  (The walk synchronises the stream, so the checking build cannot be captured into
+ * a CUDA graph.)  fsb_bounds_check_report() then gives out[0..4] = {violations seen, FSB_BAD_* kind of the first one
+ * recorded, its position in its array, the value found, the limit it broke} of the last refused call and clears the
+ * record.  In the ordinary build fsb_bounds_check_enabled() is 0 and the report returns FSB_EINVAL.
+ */
+#define FSB_BAD_COLUMN 1              /* indices[position] outside [0, n_cols)                       */
+#define FSB_BAD_ROW_POINTER 2         /* indptr[position] outside [0, nnz]                           */
+#define FSB_ROW_POINTER_DECREASES 3   /* indptr[position] < indptr[position - 1] (the limit)         */
+#define FSB_BAD_ROW_ID 4              /* row_ids[position] outside [0, n_rows)                       */
+#define FSB_BAD_SLOT_ROW 5            /* accumulator of slot `position` beyond the spare accumulator */
+#define FSB_BAD_SLOT_COLUMN 6         /* x slot of slot `position` >= n_buffers * chunk_cols         */
+#define FSB_BAD_CHUNK 7               /* unit_chunk[position] * chunk_cols >= n_cols                 */
+#define FSB_BAD_UNIT_TABLE 8          /* a unit / piece pointer table that is negative or decreases  */
+int fsb_bounds_check_enabled(void);
+int fsb_bounds_check_report(int64_t* out);
 
 #ifdef __cplusplus
 }

@@ -45,6 +45,23 @@ def test_library_exports_every_declared_symbol(fsb_lib):
     assert fsb_lib.fsb_spmm_csr_scratch_bytes(_lib.FSB_F64, 1025, 7) >= 2 * 2 * 7 * 8
 
 
+def test_checking_build_exports_the_same_symbols(fsb_lib):
+    """libfsb_check.so (the sources with -DFSB_BOUNDS_CHECK) has the same ABI; the two builds tell themselves apart."""
+    from flagsparse_b200 import build
+
+    check = ctypes.CDLL(build.build(check=True))
+    for name in _lib.SIGNATURES:
+        assert hasattr(check, name), name
+    assert check.fsb_bounds_check_enabled() == 1 and fsb_lib.fsb_bounds_check_enabled() == 0
+    out = (ctypes.c_int64 * 5)(1, 2, 3, 4, 5)
+    assert fsb_lib.fsb_bounds_check_report(ctypes.cast(out, ctypes.c_void_p)) == -1 and list(out) == [0] * 5
+    check.fsb_bounds_check_report.argtypes = [ctypes.c_void_p]
+    assert check.fsb_bounds_check_report(ctypes.cast(out, ctypes.c_void_p)) == 0 and list(out) == [0] * 5
+    assert check.fsb_bounds_check_report(None) == -1
+    with pytest.raises(RuntimeError, match="FSB_EINVAL"):
+        _lib.check(-1, "x")
+
+
 def test_argument_errors_are_reported_before_any_launch(fsb_lib):
     # bad enums / sizes are rejected on the host, so this needs no device
     assert fsb_lib.fsb_spmv_csr(7, 0, 0, None, None, None, None, None, 1, 1, 0, 0, 0, None, None, 0, None) == -1
