@@ -205,7 +205,12 @@ class ShardedCsrSpmv(_ShardedBase):
             self._setup_symmetric(1)
         if mode == "peer":
             self._plan_slices()
-        if mode == "nccl" and local_spmv is None and dist.is_initialized() and dist.get_backend(group) == "nccl":
+        # Gathering slice j while slice j + 1 is computed is there to be measured (FSB_NCCL_CHUNKS=1), not the default:
+        # NCCL's kernels need SMs and the panel kernel holds all of them until a wave of row blocks ends, so the
+        # chunked form came out slower than one all-gather after the shard (2 GPUs 2.93 against 2.82 ms, 4 GPUs 2.45
+        # against 1.91 ms on the 2.1 G-entry benchmark matrix)
+        if mode == "nccl" and local_spmv is None and dist.is_initialized() and dist.get_backend(group) == "nccl" \
+                and os.environ.get("FSB_NCCL_CHUNKS", "") not in ("", "0"):
             self._plan_nccl_chunks()
 
     def _plan_slices(self):

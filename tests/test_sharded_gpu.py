@@ -35,7 +35,7 @@ def test_single_rank(cuda, fsb_lib):
 
 
 SPMV_CASES = (("nccl", None), ("peer", None), ("fused", None), ("fused", "stream"), ("peer", "panel"),
-              ("nccl", "panel"), ("peer", "stream"))
+              ("nccl", "panel"), ("nccl-chunks", "panel"), ("peer", "stream"))
 
 
 def _worker(rank, world, port, result_dir):
@@ -57,10 +57,16 @@ def _worker(rank, world, port, result_dir):
         for mode, algo in SPMV_CASES:
             if algo:
                 os.environ["FSB_SPMV_ALGO"] = algo
+            if mode == "nccl-chunks":                   # slice j gathered while slice j + 1 is computed
+                os.environ["FSB_NCCL_CHUNKS"] = "1"
             try:
-                op = ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=mode)
+                op = ShardedCsrSpmv(d, i, p, r0, (spec.n_rows, spec.n_cols), mode=mode.split("-")[0])
             finally:
                 os.environ.pop("FSB_SPMV_ALGO", None)
+                os.environ.pop("FSB_NCCL_CHUNKS", None)
+            assert (op._nccl_chunks is not None) == (mode == "nccl-chunks")
+            if mode == "nccl-chunks":
+                assert len(op._nccl_chunks) > 1
             if (mode, algo) == ("peer", "panel"):
                 assert len(op._slices) > 1, op._slices       # slices pushed while later ones are computed
             y = None
@@ -72,6 +78,7 @@ def _worker(rank, world, port, result_dir):
         assert torch.equal(results[("nccl", None)], results[("peer", None)])
         assert torch.equal(results[("nccl", None)], results[("fused", None)])
         assert torch.equal(results[("nccl", "panel")], results[("peer", "panel")])
+        assert torch.equal(results[("nccl-chunks", "panel")], results[("peer", "panel")])
         assert torch.equal(results[("fused", "stream")], results[("peer", "stream")])
         # other kernels add in another order: held to the oracle bound by the parent, close to each other here
         assert torch.allclose(results[("nccl", None)], results[("fused", "stream")], rtol=1e-4, atol=1e-4)
