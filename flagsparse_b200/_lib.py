@@ -77,6 +77,13 @@ SIGNATURES = {
     "fsb_spmm_csr_wide": (_i32, [_i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _vp]),
     "fsb_sddmm_csr": (_i32, [_i32, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, _c.c_double,
                              _c.c_double, _vp]),
+    "fsb_panel_build_max_chunks": (_i32, []),
+    "fsb_panel_build_count": (_i32, [_i32, _i32, _vp, _vp, _i64, _i64, _i32, _i32, _vp, _vp]),
+    "fsb_panel_build_sort": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsb_panel_build_runs": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "fsb_panel_build_cut": (_i32, [_vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
+    "fsb_panel_build_fill": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp,
+                                    _vp]),
     "fsb_bounds_check_enabled": (_i32, []),
     "fsb_bounds_check_report": (_i32, [_vp]),
 }

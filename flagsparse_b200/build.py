@@ -17,7 +17,7 @@ INCLUDE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 LIB = os.path.join(CSRC, "libfsb.so")
 CHECK_LIB = os.path.join(CSRC, "libfsb_check.so")
 SOURCES = ("csr_analyze.cu", "spmv_csr.cu", "spmv_panel.cu", "spmv_wide.cu", "spmm_csr.cu", "sddmm_csr.cu",
-           "bounds_check.cu")
+           "bounds_check.cu", "panel_build.cu")
 NVCC_FLAGS = (
     "-O3",
     "-std=c++17",

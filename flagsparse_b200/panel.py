@@ -376,6 +376,108 @@ def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slo
     return val, rc, upiece, u_ch, u_rb, n_pieces, max_run, n_runs
 
 
+FUSED_MAX_TABLE = 1 << 24    # (row blocks x column chunks) cells the device-side builder keeps a dense table of
+_ITYPE = {torch.int32: _lib.FSB_I32, torch.int64: _lib.FSB_I64}
+
+
+def _fused_applicable(data, indices, indptr, n_rows, n_cols, RB, CW):
+    # FSB_PANEL_BUILDER=torch keeps the host-side builder (what the tests compare the device-side one with)
+    if os.environ.get("FSB_PANEL_BUILDER", "") == "torch" or data.device.type != "cuda":
+        return False
+    if indices.dtype not in _ITYPE or indptr.dtype not in _ITYPE or data.numel() >= 2**31 - 1:
+        return False
+    n_rb, n_ch = -(-n_rows // RB), -(-n_cols // CW)
+    return n_ch <= int(_lib.lib().fsb_panel_build_max_chunks()) and n_rb * n_ch <= FUSED_MAX_TABLE
+
+
+def _build_fused(data, indices, indptr, n_rows, n_cols, geometry, NB, rounds, force):
+    """The layout built by the kernels of csrc/panel_build.cu (count, sort, runs, cut, fill) with three host
+    synchronisations, bit-identical to what _build_slab + pack_pieces give.  Returns a PanelLayout; None when the
+    matrix should not (or cannot) take the panel kernel; or the string "host" when the host-side builder has to do
+    it: entries of a tile spread over too many chunks for the sort pass, or a float32 matrix with mostly one entry
+    per row and unit, whose core pieces (pack_pieces_core) only the host-side builder makes."""
+    L = _lib.lib()
+    vt, sv, CW, RB = geometry
+    dev = data.device
+    nnz = data.numel()
+    n_rb, n_ch = -(-n_rows // RB), -(-n_cols // CW)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    it, pt = _ITYPE[indices.dtype], _ITYPE[indptr.dtype]
+    data, indices, indptr = data.contiguous(), indices.contiguous(), indptr.contiguous()
+    with torch.cuda.device(dev):
+        cnt = torch.empty(n_rb * n_ch, dtype=torch.int32, device=dev)
+        _lib.check(L.fsb_panel_build_count(it, pt, indices.data_ptr(), indptr.data_ptr(), n_rows, n_cols, RB, CW,
+                                           cnt.data_ptr(), st), "fsb_panel_build_count")
+        cell = torch.nonzero(cnt, as_tuple=False).flatten()          # units in (row block, chunk) order; a sync
+        n_units = cell.numel()
+        limit = MAX_X_OVERHEAD if sv == 4 else MAX_X_OVERHEAD_F64
+        if not force and n_units * CW * sv > limit * nnz * (sv + 4):
+            return None
+        ustart = _cumsum0(cnt[cell].to(torch.int64)).to(torch.int32)
+        unit_base = torch.zeros(n_rb * n_ch, dtype=torch.int32, device=dev)
+        unit_base[cell] = ustart[:-1]
+        u_rb = (cell // n_ch).to(torch.int32)
+        u_ch = (cell % n_ch).to(torch.int32)
+        rb_unit_ptr = _cumsum0(torch.bincount(cell // n_ch, minlength=n_rb)).to(torch.int32)
+        s_val = torch.empty(nnz, dtype=data.dtype, device=dev)
+        s_row = torch.empty(nnz, dtype=torch.int32, device=dev)
+        s_col = torch.empty(nnz, dtype=torch.int32, device=dev)
+        flag = torch.zeros(2, dtype=torch.int32, device=dev)
+        stats = torch.empty(5, dtype=torch.int64, device=dev)
+        _lib.check(L.fsb_panel_build_sort(vt, it, pt, data.data_ptr(), indices.data_ptr(), indptr.data_ptr(), n_rows,
+                                          n_cols, RB, CW, unit_base.data_ptr(), s_val.data_ptr(), s_row.data_ptr(),
+                                          s_col.data_ptr(), flag.data_ptr(), st), "fsb_panel_build_sort")
+        _lib.check(L.fsb_panel_build_runs(s_row.data_ptr(), s_col.data_ptr(), nnz, CW, stats.data_ptr(), st),
+                   "fsb_panel_build_runs")
+        del unit_base, cnt
+        failed = int(flag[0].item())                                  # a sync
+        n_runs, max_run, *long_runs = (int(v) for v in stats.tolist())
+        if failed:
+            return "host"
+        if sv == 4 and nnz < RUNS_MIN_MEAN * n_runs and not os.environ.get("FSB_PANEL_NO_CORE"):
+            return "host"
+        rounds = rounds or choose_rounds(long_runs)
+        while True:
+            SLOTS = 32 * rounds
+            packed = None
+            if max_run <= SLOTS:
+                pcount = torch.empty(n_units, dtype=torch.int32, device=dev)
+                _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, None,
+                                                 pcount.data_ptr(), None, flag[1:].data_ptr(), st),
+                           "fsb_panel_build_cut")
+                upiece = _cumsum0(pcount.to(torch.int64))
+                n_pieces = int(upiece[-1].item())                     # a sync
+                if n_pieces < 2**31 - 1 and (force or n_pieces * SLOTS <= MAX_SLOT_OVERHEAD * nnz + 4096):
+                    packed = upiece.to(torch.int32)
+            if packed is not None:
+                break
+            if rounds == ROUNDS[-1]:
+                return None
+            rounds = ROUNDS[-1]      # a run that does not fit a small piece, or too much padding
+        upiece = packed
+        pstart = torch.empty(n_pieces + 1, dtype=torch.int32, device=dev)
+        pstart[-1] = nnz
+        _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, upiece.data_ptr(), None,
+                                         pstart.data_ptr(), flag[1:].data_ptr(), st), "fsb_panel_build_cut")
+        val = torch.empty(n_pieces * SLOTS, dtype=data.dtype, device=dev)
+        rc = torch.empty(n_pieces * SLOTS, dtype=torch.int32, device=dev)
+        _lib.check(L.fsb_panel_build_fill(vt, s_val.data_ptr(), s_row.data_ptr(), s_col.data_ptr(), pstart.data_ptr(),
+                                          upiece.data_ptr(), n_units, u_rb.data_ptr(), rb_unit_ptr.data_ptr(), n_pieces,
+                                          RB, CW, NB, rounds, val.data_ptr(), rc.data_ptr(), st),
+                   "fsb_panel_build_fill")
+    lay = PanelLayout()
+    lay.val, lay.rc = val, rc
+    lay.unit_piece_ptr, lay.unit_chunk, lay.rb_unit_ptr = upiece, u_ch, rb_unit_ptr
+    lay.n_row_blocks, lay.rb_rows, lay.chunk_cols, lay.n_buffers = n_rb, RB, CW, NB
+    lay.rounds, lay.max_run, lay.pad_row = rounds, max_run, RB
+    lay.flags = (FLAG_LONG_RUNS if max_run > rounds else 0) | (FLAG_RUNS if nnz >= RUNS_MIN_MEAN * n_runs else 0)
+    lay.n_units, lay.n_pieces = n_units, n_pieces
+    lay.x_overhead = n_units * CW * sv / float(nnz * (sv + 4))
+    lay.slot_overhead = n_pieces * SLOTS / float(nnz)
+    lay.status = StatusWord(dev)
+    return lay
+
+
 def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force=False, rounds=None):
     """PanelLayout for the matrix, or None when the panel kernel would not pay (or cannot be used)."""
     nnz = data.numel()
@@ -392,6 +494,10 @@ def build_panel_layout(data, indices, indptr, n_rows, n_cols, max_row_nnz, force
     n_rb = -(-n_rows // RB)
     n_ch = -(-n_cols // CW)
     rounds = rounds or default_rounds()
+    if _fused_applicable(data, indices, indptr, n_rows, n_cols, RB, CW):
+        lay = _build_fused(data, indices, indptr, n_rows, n_cols, geometry, NB, rounds, force)
+        if not isinstance(lay, str):
+            return lay
     if not force or rounds is None:
         scan = scan_structure(indices, indptr, n_rows, n_cols, RB, CW)
         if scan is None:

@@ -221,6 +221,41 @@ int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, co
  *     partial sums: serialise them.
  * Results are bit-identical to fsb_spmv_csr(FSB_SPMV_STREAM) with the same tuning.
  */
+/*
+ * Construction of the panel layout on the device (the reference has no counterpart: its prepare step builds row
+ * buckets, spmv_csr.py:281-327).  Five passes, called in this order by flagsparse_b200/panel.py, every array caller-owned:
+ *   count  cnt[rb * n_ch + c] = entries of row block rb (rb_rows rows) in column chunk c (chunk_cols columns);
+ *          n_ch = ceil(n_cols / chunk_cols) <= fsb_panel_build_max_chunks()
+ *   sort   the entries in unit order (units = non-empty (rb, c) cells in row-major cell order; inside a unit the CSR
+ *          order is kept): sorted_val / sorted_row (global row) / sorted_col (global column), nnz < 2^31 elements each;
+ *          unit_base[rb * n_ch + c] = position of the unit's first entry.  *status (device int32) is set to 1 when 1024
+ *          consecutive entries of the matrix span more than 128 chunks -- the caller then falls back to another builder
+ *   runs   stats[0..4] (device int64) = runs (consecutive sorted entries of one row in one unit), longest run, runs
+ *          longer than 4 / 8 / 16 entries
+ *   cut    greedy cuts of every unit into pieces of at most `slots` entries that split no run.  With piece_start ==
+ *          NULL: piece_count[u] = pieces of unit u.  With piece_start: piece_start[unit_piece_ptr[u] + k] = first sorted
+ *          entry of the k-th piece of unit u (the caller sets piece_start[n_pieces] = nnz).  *status = 2 when a run is
+ *          longer than a piece
+ *   fill   val / rc of fsb_spmv_csr_panel (n_pieces * 32 * rounds slots): per piece, entries in stable order of
+ *          (local row mod 32 for float32, mod 16 for float64), slot s of that order in lane s / rounds, round s % rounds;
+ *          unit_rb[u] = row block of unit u; unused slots carry value 0 and the spare accumulator rb_rows
+ */
+int fsb_panel_build_max_chunks(void);
+int fsb_panel_build_count(int itype, int ptype, const void* indices, const void* indptr, int64_t n_rows,
+                          int64_t n_cols, int32_t rb_rows, int32_t chunk_cols, int32_t* cnt, void* stream);
+int fsb_panel_build_sort(int vtype, int itype, int ptype, const void* data, const void* indices, const void* indptr,
+                         int64_t n_rows, int64_t n_cols, int32_t rb_rows, int32_t chunk_cols, const int32_t* unit_base,
+                         void* sorted_val, int32_t* sorted_row, int32_t* sorted_col, int32_t* status, void* stream);
+int fsb_panel_build_runs(const int32_t* sorted_row, const int32_t* sorted_col, int64_t nnz, int32_t chunk_cols,
+                         int64_t* stats, void* stream);
+int fsb_panel_build_cut(const int32_t* sorted_row, const int32_t* unit_start, int32_t n_units, int32_t slots,
+                        const int32_t* unit_piece_ptr, int32_t* piece_count, int32_t* piece_start, int32_t* status,
+                        void* stream);
+int fsb_panel_build_fill(int vtype, const void* sorted_val, const int32_t* sorted_row, const int32_t* sorted_col,
+                         const int32_t* piece_start, const int32_t* unit_piece_ptr, int32_t n_units,
+                         const int32_t* unit_rb, const int32_t* rb_unit_ptr, int32_t n_pieces, int32_t rb_rows,
+                         int32_t chunk_cols, int32_t n_buffers, int32_t rounds, void* val, uint32_t* rc, void* stream);
+
 #define FSB_NOALLOC_MAX_TILES 262144
 int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, const void* indices,
                          const void* indptr, const void* x, void* y, int64_t n_rows, int64_t n_cols,
