@@ -46,12 +46,19 @@ panel_count_kernel(const I* __restrict__ idx, const P* __restrict__ ptr, int64_t
   for (int i = tid; i < n_ch; i += kBuildThreads) s_cnt[i] = 0;
   __syncthreads();
   const int64_t e0 = (int64_t)ptr[r0], e1 = (int64_t)ptr[r1];
-  for (int64_t base = e0; base < e1; base += kBuildThreads) {
-    const int64_t e = base + tid;
-    const bool live = e < e1;
-    const int c = live ? chunk_of(idx[e], chunk_cols) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, c);
-    if (live && lane == __ffs(peers) - 1) atomicAdd(&s_cnt[c], __popc(peers));
+  constexpr int U = 4;                                  // tiles whose loads are in flight together
+  for (int64_t base = e0; base < e1; base += U * kBuildThreads) {
+    int c[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int64_t e = base + k * kBuildThreads + tid;
+      c[k] = e < e1 ? chunk_of(idx[e], chunk_cols) : -1;
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const unsigned peers = __match_any_sync(0xffffffffu, c[k]);
+      if (c[k] >= 0 && lane == __ffs(peers) - 1) atomicAdd(&s_cnt[c[k]], __popc(peers));
+    }
   }
   __syncthreads();
   int32_t* out = cnt + (int64_t)blockIdx.x * n_ch;
@@ -67,16 +74,22 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
                   V* __restrict__ o_val, int32_t* __restrict__ o_row, int32_t* __restrict__ o_col,
                   int32_t* __restrict__ status) {
   extern __shared__ int32_t s_run[];                      // next free position of every unit of this row block
-  __shared__ uint16_t s_cntw[kBuildWarps][kBuildWindow];  // entries of (warp, chunk) in the tile, then their prefix
+  // entries of (warp, chunk) in the tile, then their prefix over the warps; rows padded by one 32-bit word so that
+  // a column (one chunk, all warps) falls into 32 different banks
+  __shared__ uint16_t s_cntw[kBuildWarps][kBuildWindow + 2];
   __shared__ int32_t s_tile_base[kBuildWindow];
   __shared__ int s_min[kBuildWarps];
   __shared__ int s_tmin, s_fail;
+  __shared__ long long s_tile_row;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t r0 = (int64_t)blockIdx.x * rb_rows;
   const int64_t r1 = (r0 + rb_rows) < n_rows ? (r0 + rb_rows) : n_rows;
   const int32_t* base_row = unit_base + (int64_t)blockIdx.x * n_ch;
   for (int i = tid; i < n_ch; i += kBuildThreads) s_run[i] = base_row[i];
-  if (tid == 0) s_fail = 0;
+  if (tid == 0) {
+    s_fail = 0;
+    s_tile_row = r0;
+  }
   __syncthreads();
   const int64_t e0 = (int64_t)ptr[r0], e1 = (int64_t)ptr[r1];
   for (int64_t base = e0; base < e1; base += kBuildThreads) {
@@ -86,7 +99,7 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
     const int c = live ? chunk_of(col, chunk_cols) : INT_MAX;
     const int wm = warp_min_i(c);
     if (lane == 0) s_min[warp] = wm;
-    for (int i = tid; i < kBuildWarps * kBuildWindow; i += kBuildThreads) (&s_cntw[0][0])[i] = 0;
+    for (int i = tid; i < kBuildWarps * (kBuildWindow + 2); i += kBuildThreads) (&s_cntw[0][0])[i] = 0;
     __syncthreads();
     if (warp == 0) {
       const int m = warp_min_i(s_min[lane]);
@@ -94,6 +107,7 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
     }
     __syncthreads();
     const int tmin = s_tmin;
+    const int64_t tile_row = s_tile_row;
     const int b = live ? (c - tmin) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, b);
     const int rank = __popc(peers & ((1u << lane) - 1u));
@@ -103,23 +117,35 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
     }
     __syncthreads();
     if (s_fail) break;                                   // the same answer for every thread
-    if (tid < kBuildWindow) {
-      int acc = 0;
-      for (int w = 0; w < kBuildWarps; ++w) {
-        const int t = s_cntw[w][tid];
-        s_cntw[w][tid] = (uint16_t)acc;
-        acc += t;
+    // per chunk of the window: exclusive prefix of the 32 warps' counts (lane = source warp), then the unit's
+    // running offset moves on by the total; warp w looks after chunks w, w + 32, ...
+    for (int bin = warp; bin < kBuildWindow; bin += kBuildWarps) {
+      const int mine = s_cntw[lane][bin];
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += other;
       }
-      if (acc > 0) {
-        s_tile_base[tid] = s_run[tmin + tid];
-        s_run[tmin + tid] += acc;
+      s_cntw[lane][bin] = (uint16_t)(incl - mine);
+      if (lane == 31 && incl > 0) {
+        s_tile_base[bin] = s_run[tmin + bin];
+        s_run[tmin + bin] += incl;
       }
     }
     __syncthreads();
     if (live) {
       const int64_t pos = (int64_t)s_tile_base[b] + s_cntw[warp][b] + rank;
-      // the row that holds entry e: the last row r of the block with ptr[r] <= e
-      int64_t lo = r0, hi = r1 - 1;
+      // the row that holds entry e: the last row r of the block with ptr[r] <= e.  It is not in front of the row
+      // of the tile's first entry, and seldom far behind it: gallop from there, then bisect
+      int64_t lo = tile_row, hi = r1 - 1;
+      for (int64_t step = 32; lo + step < hi; step <<= 1) {
+        if ((int64_t)ptr[lo + step] > e) {
+          hi = lo + step - 1;
+          break;
+        }
+        lo += step;
+      }
       while (lo < hi) {
         const int64_t mid = (lo + hi + 1) >> 1;
         if ((int64_t)ptr[mid] <= e) lo = mid;
@@ -128,6 +154,7 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
       o_val[pos] = data[e];
       o_row[pos] = (int32_t)lo;
       o_col[pos] = (int32_t)col;
+      if (tid == kBuildThreads - 1) s_tile_row = lo;   // the next tile's entries are in this row or behind it
     }
     __syncthreads();   // the tables are rewritten by the next tile
   }
@@ -148,6 +175,7 @@ __global__ void __launch_bounds__(kBuildThreads)
 panel_runs_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ col, int64_t nnz, int chunk_cols,
                   int tiles_per_cta, unsigned long long* __restrict__ stats) {
   __shared__ long long s_warp_last[kBuildWarps];
+  __shared__ long long s_before[kBuildWarps];
   __shared__ long long s_carry;
   __shared__ unsigned long long s_acc[5];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -174,8 +202,20 @@ panel_runs_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ c
     }
     if (lane == 31) s_warp_last[warp] = last;
     __syncthreads();
-    long long before = s_carry;                        // the last start in front of this warp
-    for (int w = 0; w < warp; ++w) before = s_warp_last[w] > before ? s_warp_last[w] : before;
+    if (warp == 0) {                                   // s_before[w] = the last start in front of warp w
+      long long v = s_warp_last[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const long long other = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o && other > v) v = other;
+      }
+      const long long carry = s_carry;
+      long long excl = __shfl_up_sync(0xffffffffu, v, 1);
+      if (lane == 0 || excl < carry) excl = carry;
+      s_before[lane] = excl;
+    }
+    __syncthreads();
+    const long long before = s_before[warp];
     if (last < before) last = before;
     if (live) {
       const unsigned long long d = (unsigned long long)(e - last);   // entries of the run in front of e
