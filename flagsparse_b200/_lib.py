@@ -79,7 +79,12 @@ SIGNATURES = {
                              _c.c_double, _vp]),
     "fsb_panel_build_max_chunks": (_i32, []),
     "fsb_panel_build_count": (_i32, [_i32, _i32, _vp, _vp, _i64, _i64, _i32, _i32, _vp, _vp]),
-    "fsb_panel_build_sort": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "fsb_panel_build_sort": (_i32, [_i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp,
+                                    _vp]),
+    "fsb_panel_build_window": (_i32, [_i32]),
+    "fsb_panel_build_core_count": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "fsb_panel_build_core_place": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp,
+                                          _vp, _vp, _vp, _vp, _vp, _vp]),
     "fsb_panel_build_runs": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "fsb_panel_build_cut": (_i32, [_vp, _vp, _i32, _i32, _vp, _vp, _vp, _vp, _vp]),
     "fsb_panel_build_fill": (_i32, [_i32, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp,

@@ -20,7 +20,8 @@ namespace fsb {
 
 constexpr int kBuildThreads = 1024;
 constexpr int kBuildWarps = kBuildThreads / 32;
-constexpr int kBuildWindow = 128;      // distinct chunks a tile of 1024 consecutive entries may span
+constexpr int kBuildWindowSmall = 128; // distinct chunks a tile of 1024 consecutive entries may span: narrow bands
+constexpr int kBuildWindowLarge = 640; // ... and wide ones (more table to clear and to scan per tile)
 constexpr int kBuildMaxChunks = 32768; // the count pass keeps one counter per chunk in shared memory
 
 __device__ __forceinline__ int warp_min_i(int v) {
@@ -67,7 +68,7 @@ panel_count_kernel(const I* __restrict__ idx, const P* __restrict__ ptr, int64_t
 
 // ---- sort ----------------------------------------------------------------------------------------
 // unit_base[rb * n_ch + c] = position of the first entry of unit (rb, c) in the sorted arrays
-template <typename V, typename I, typename P>
+template <typename V, typename I, typename P, int kBuildWindow>
 __global__ void __launch_bounds__(kBuildThreads, 1)
 panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P* __restrict__ ptr, int64_t n_rows,
                   int rb_rows, int chunk_cols, int n_ch, const int32_t* __restrict__ unit_base,
@@ -289,7 +290,7 @@ template <typename V>
 __global__ void __launch_bounds__(kFillWarps * 32)
 panel_fill_kernel(const V* __restrict__ s_val, const int32_t* __restrict__ s_row, const int32_t* __restrict__ s_col,
                   const int32_t* __restrict__ piece_start, const int32_t* __restrict__ unit_piece_ptr, int n_units,
-                  const int32_t* __restrict__ unit_rb, const int32_t* __restrict__ rb_unit_ptr, int n_pieces,
+                  const int32_t* __restrict__ unit_rb, const int32_t* __restrict__ unit_ord, int n_pieces,
                   int rb_rows, int chunk_cols, int n_buffers, int rounds, int banks, uint32_t pad_row,
                   V* __restrict__ val, uint32_t* __restrict__ rc) {
   __shared__ int s_bank[kFillWarps][32];
@@ -308,7 +309,7 @@ panel_fill_kernel(const V* __restrict__ s_val, const int32_t* __restrict__ s_row
   }
   const int u = lo;
   const int rb = unit_rb[u];
-  const int x_base = ((u - rb_unit_ptr[rb]) % n_buffers) * chunk_cols;
+  const int x_base = (unit_ord[u] % n_buffers) * chunk_cols;
   const int64_t row0 = (int64_t)rb * rb_rows;
   constexpr int E = 16 / (int)sizeof(V);
   int* bank_pos = s_bank[warp];
@@ -367,6 +368,109 @@ panel_fill_kernel(const V* __restrict__ s_val, const int32_t* __restrict__ s_row
   }
 }
 
+// ---- core pieces ---------------------------------------------------------------------------------
+// For layouts in which most rows have one entry per unit: the entries that are alone in their run ("singles") are
+// listed per class (local row mod 32) in unit order; with J = (shortest list) / rounds, the first J * rounds singles of
+// every class fill J core pieces of the unit completely (piece j takes entries j * rounds .. of every list, lane =
+// class), so that the 32 accumulators of a round lie in 32 different banks.  Everything else (the "rest") keeps its
+// order and is cut and filled like an ordinary unit.  One warp per unit, entries taken 32 at a time in unit order.
+constexpr int kCoreWarps = 8;
+
+__device__ __forceinline__ bool single_at(const int32_t* __restrict__ row, int64_t e, int64_t u0, int64_t u1) {
+  const int32_t r = row[e];
+  return (e == u0 || row[e - 1] != r) && (e + 1 == u1 || row[e + 1] != r);
+}
+
+__global__ void __launch_bounds__(kCoreWarps * 32)
+panel_core_count_kernel(const int32_t* __restrict__ s_row, const int32_t* __restrict__ unit_start,
+                        const int32_t* __restrict__ unit_rb, int n_units, int rb_rows, int rounds,
+                        int32_t* __restrict__ core_pieces, int32_t* __restrict__ rest_count) {
+  __shared__ int s_cls[kCoreWarps][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int u = blockIdx.x * kCoreWarps + warp;
+  if (u >= n_units) return;
+  const int64_t u0 = unit_start[u], u1 = unit_start[u + 1];
+  const int64_t row0 = (int64_t)unit_rb[u] * rb_rows;
+  int* cls_n = s_cls[warp];
+  cls_n[lane] = 0;
+  __syncwarp();
+  for (int64_t e0 = u0; e0 < u1; e0 += 32) {
+    const int64_t e = e0 + lane;
+    int key = -1;
+    if (e < u1 && single_at(s_row, e, u0, u1)) key = (int)((s_row[e] - row0) & 31);
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    if (key >= 0 && lane == __ffs(peers) - 1) cls_n[key] += __popc(peers);
+    __syncwarp();
+  }
+  int m = cls_n[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = min(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) {
+    const int j = m / rounds;
+    core_pieces[u] = j;
+    rest_count[u] = (int)(u1 - u0) - j * rounds * 32;
+  }
+}
+
+template <typename V>
+__global__ void __launch_bounds__(kCoreWarps * 32)
+panel_core_place_kernel(const V* __restrict__ s_val, const int32_t* __restrict__ s_row,
+                        const int32_t* __restrict__ s_col, const int32_t* __restrict__ unit_start,
+                        const int32_t* __restrict__ unit_rb, const int32_t* __restrict__ unit_ord, int n_units,
+                        int rb_rows, int chunk_cols, int n_buffers, int rounds,
+                        const int32_t* __restrict__ core_pieces, const int32_t* __restrict__ core_base,
+                        const int32_t* __restrict__ rest_start, V* __restrict__ core_val,
+                        uint32_t* __restrict__ core_rc, V* __restrict__ rest_val, int32_t* __restrict__ rest_row,
+                        int32_t* __restrict__ rest_col) {
+  __shared__ int s_cls[kCoreWarps][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int u = blockIdx.x * kCoreWarps + warp;
+  if (u >= n_units) return;
+  const int64_t u0 = unit_start[u], u1 = unit_start[u + 1];
+  const int64_t row0 = (int64_t)unit_rb[u] * rb_rows;
+  const int x_base = (unit_ord[u] % n_buffers) * chunk_cols;
+  const int core_entries = core_pieces[u] * rounds;          // per class
+  const size_t piece0 = (size_t)core_base[u];
+  const int slots = 32 * rounds;
+  constexpr int E = 16 / (int)sizeof(V);
+  int64_t rest_pos = rest_start[u];
+  int* cls_pos = s_cls[warp];
+  cls_pos[lane] = 0;
+  __syncwarp();
+  for (int64_t e0 = u0; e0 < u1; e0 += 32) {
+    const int64_t e = e0 + lane;
+    const bool live = e < u1;
+    int key = -1, acc = 0, col = 0;
+    V v = (V)0;
+    if (live) {
+      acc = (int)(s_row[e] - row0);
+      col = s_col[e];
+      v = s_val[e];
+      if (single_at(s_row, e, u0, u1)) key = acc & 31;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    const int rank = key >= 0 ? cls_pos[key] + __popc(peers & ((1u << lane) - 1u)) : 0;
+    __syncwarp();
+    if (key >= 0 && lane == __ffs(peers) - 1) cls_pos[key] += __popc(peers);
+    __syncwarp();
+    const bool core = key >= 0 && rank < core_entries;
+    const unsigned rest_mask = __ballot_sync(0xffffffffu, live && !core);
+    if (core) {
+      const int k = rank % rounds;
+      const size_t base = (piece0 + (size_t)(rank / rounds)) * slots;
+      core_val[base + (size_t)(k / E) * (32 * E) + key * E + k % E] = v;
+      core_rc[base + (size_t)(k >> 2) * 128 + key * 4 + (k & 3)] =
+          ((uint32_t)acc << 16) | (uint32_t)(x_base + (int)((uint32_t)col % (uint32_t)chunk_cols));
+    } else if (live) {
+      const int64_t at = rest_pos + __popc(rest_mask & ((1u << lane) - 1u));
+      rest_val[at] = v;
+      rest_row[at] = s_row[e];
+      rest_col[at] = col;
+    }
+    rest_pos += __popc(rest_mask);
+  }
+}
+
 static bool build_types_ok(int vtype, int itype, int ptype) {
   return (vtype == FSB_F32 || vtype == FSB_F64) && (itype == FSB_I32 || itype == FSB_I64) &&
          (ptype == FSB_I32 || ptype == FSB_I64);
@@ -408,8 +512,8 @@ extern "C" int fsb_panel_build_count(int itype, int ptype, const void* indices, 
 
 extern "C" int fsb_panel_build_sort(int vtype, int itype, int ptype, const void* data, const void* indices,
                                     const void* indptr, int64_t n_rows, int64_t n_cols, int32_t rb_rows,
-                                    int32_t chunk_cols, const int32_t* unit_base, void* sorted_val, int32_t* sorted_row,
-                                    int32_t* sorted_col, int32_t* status, void* stream_) {
+                                    int32_t chunk_cols, int32_t wide_window, const int32_t* unit_base, void* sorted_val,
+                                    int32_t* sorted_row, int32_t* sorted_col, int32_t* status, void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (!build_types_ok(vtype, itype, ptype) || n_rows < 0 || n_cols < 0 || rb_rows <= 0 || chunk_cols <= 0)
     return FSB_EINVAL;
@@ -420,14 +524,19 @@ extern "C" int fsb_panel_build_sort(int vtype, int itype, int ptype, const void*
   const int64_t n_rb = (n_rows + rb_rows - 1) / rb_rows;
   if (n_ch > kBuildMaxChunks || n_rb >= INT32_MAX || n_cols >= INT32_MAX) return FSB_ERANGE;
   const size_t smem = (size_t)n_ch * sizeof(int32_t);
-#define FSB_SORT_(V_, I_, P_)                                                                                       \
-  do {                                                                                                              \
-    cudaError_t e = cudaFuncSetAttribute(panel_sort_kernel<V_, I_, P_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                                \
-    if (e != cudaSuccess) return cuda_rc(e);                                                                        \
-    panel_sort_kernel<V_, I_, P_><<<(unsigned)n_rb, kBuildThreads, smem, st>>>(                                     \
-        (const V_*)data, (const I_*)indices, (const P_*)indptr, n_rows, rb_rows, chunk_cols, (int)n_ch, unit_base,  \
-        (V_*)sorted_val, sorted_row, sorted_col, status);                                                           \
+#define FSB_SORT_W_(V_, I_, P_, W_)                                                                                  \
+  do {                                                                                                               \
+    cudaError_t e = cudaFuncSetAttribute(panel_sort_kernel<V_, I_, P_, W_>,                                          \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                    \
+    if (e != cudaSuccess) return cuda_rc(e);                                                                         \
+    panel_sort_kernel<V_, I_, P_, W_><<<(unsigned)n_rb, kBuildThreads, smem, st>>>(                                  \
+        (const V_*)data, (const I_*)indices, (const P_*)indptr, n_rows, rb_rows, chunk_cols, (int)n_ch, unit_base,   \
+        (V_*)sorted_val, sorted_row, sorted_col, status);                                                            \
+  } while (0)
+#define FSB_SORT_(V_, I_, P_)                                      \
+  do {                                                             \
+    if (wide_window) FSB_SORT_W_(V_, I_, P_, kBuildWindowLarge);   \
+    else FSB_SORT_W_(V_, I_, P_, kBuildWindowSmall);               \
   } while (0)
 #define FSB_SORT_V_(V_)                                              \
   do {                                                               \
@@ -440,6 +549,7 @@ extern "C" int fsb_panel_build_sort(int vtype, int itype, int ptype, const void*
   else FSB_SORT_V_(double);
 #undef FSB_SORT_V_
 #undef FSB_SORT_
+#undef FSB_SORT_W_
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }
@@ -480,7 +590,7 @@ extern "C" int fsb_panel_build_cut(const int32_t* sorted_row, const int32_t* uni
 extern "C" int fsb_panel_build_fill(int vtype, const void* sorted_val, const int32_t* sorted_row,
                                     const int32_t* sorted_col, const int32_t* piece_start,
                                     const int32_t* unit_piece_ptr, int32_t n_units, const int32_t* unit_rb,
-                                    const int32_t* rb_unit_ptr, int32_t n_pieces, int32_t rb_rows, int32_t chunk_cols,
+                                    const int32_t* unit_ord, int32_t n_pieces, int32_t rb_rows, int32_t chunk_cols,
                                     int32_t n_buffers, int32_t rounds, void* val, uint32_t* rc, void* stream_) {
   cudaStream_t st = static_cast<cudaStream_t>(stream_);
   if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
@@ -488,18 +598,63 @@ extern "C" int fsb_panel_build_fill(int vtype, const void* sorted_val, const int
   if (rounds != 4 && rounds != 8 && rounds != 16) return FSB_EINVAL;
   if ((int64_t)n_buffers * chunk_cols > 65536) return FSB_EINVAL;
   if (n_pieces == 0) return FSB_OK;
-  if (!sorted_val || !sorted_row || !sorted_col || !piece_start || !unit_piece_ptr || !unit_rb || !rb_unit_ptr ||
+  if (!sorted_val || !sorted_row || !sorted_col || !piece_start || !unit_piece_ptr || !unit_rb || !unit_ord ||
       !val || !rc)
     return FSB_EINVAL;
   const unsigned g = (unsigned)((n_pieces + kFillWarps - 1) / kFillWarps);
   if (vtype == FSB_F32)
     panel_fill_kernel<float><<<g, kFillWarps * 32, 0, st>>>(
-        (const float*)sorted_val, sorted_row, sorted_col, piece_start, unit_piece_ptr, n_units, unit_rb, rb_unit_ptr,
+        (const float*)sorted_val, sorted_row, sorted_col, piece_start, unit_piece_ptr, n_units, unit_rb, unit_ord,
         n_pieces, rb_rows, chunk_cols, n_buffers, rounds, 32, (uint32_t)rb_rows, (float*)val, rc);
   else
     panel_fill_kernel<double><<<g, kFillWarps * 32, 0, st>>>(
-        (const double*)sorted_val, sorted_row, sorted_col, piece_start, unit_piece_ptr, n_units, unit_rb, rb_unit_ptr,
+        (const double*)sorted_val, sorted_row, sorted_col, piece_start, unit_piece_ptr, n_units, unit_rb, unit_ord,
         n_pieces, rb_rows, chunk_cols, n_buffers, rounds, 16, (uint32_t)rb_rows, (double*)val, rc);
+  FSB_RETURN_IF_LAUNCH_FAILED();
+  return FSB_OK;
+}
+
+extern "C" int fsb_panel_build_window(int wide) { return wide ? kBuildWindowLarge : kBuildWindowSmall; }
+
+extern "C" int fsb_panel_build_core_count(const int32_t* sorted_row, const int32_t* unit_start, const int32_t* unit_rb,
+                                          int32_t n_units, int32_t rb_rows, int32_t rounds, int32_t* core_pieces,
+                                          int32_t* rest_count, void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  if (n_units < 0 || rb_rows <= 0 || (rounds != 4 && rounds != 8 && rounds != 16)) return FSB_EINVAL;
+  if (n_units == 0) return FSB_OK;
+  if (!sorted_row || !unit_start || !unit_rb || !core_pieces || !rest_count) return FSB_EINVAL;
+  panel_core_count_kernel<<<(unsigned)((n_units + kCoreWarps - 1) / kCoreWarps), kCoreWarps * 32, 0, st>>>(
+      sorted_row, unit_start, unit_rb, n_units, rb_rows, rounds, core_pieces, rest_count);
+  FSB_RETURN_IF_LAUNCH_FAILED();
+  return FSB_OK;
+}
+
+extern "C" int fsb_panel_build_core_place(int vtype, const void* sorted_val, const int32_t* sorted_row,
+                                          const int32_t* sorted_col, const int32_t* unit_start, const int32_t* unit_rb,
+                                          const int32_t* unit_ord, int32_t n_units, int32_t rb_rows, int32_t chunk_cols,
+                                          int32_t n_buffers, int32_t rounds, const int32_t* core_pieces,
+                                          const int32_t* core_base, const int32_t* rest_start, void* core_val,
+                                          uint32_t* core_rc, void* rest_val, int32_t* rest_row, int32_t* rest_col,
+                                          void* stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  if (vtype != FSB_F32 && vtype != FSB_F64) return FSB_EINVAL;
+  if (n_units < 0 || rb_rows <= 0 || rb_rows >= 65535 || chunk_cols <= 0 || n_buffers < 1) return FSB_EINVAL;
+  if ((rounds != 4 && rounds != 8 && rounds != 16) || (int64_t)n_buffers * chunk_cols > 65536) return FSB_EINVAL;
+  if (n_units == 0) return FSB_OK;
+  if (!sorted_val || !sorted_row || !sorted_col || !unit_start || !unit_rb || !unit_ord || !core_pieces || !core_base ||
+      !rest_start || !core_val || !core_rc || !rest_val || !rest_row || !rest_col)
+    return FSB_EINVAL;
+  const unsigned g = (unsigned)((n_units + kCoreWarps - 1) / kCoreWarps);
+  if (vtype == FSB_F32)
+    panel_core_place_kernel<float><<<g, kCoreWarps * 32, 0, st>>>(
+        (const float*)sorted_val, sorted_row, sorted_col, unit_start, unit_rb, unit_ord, n_units, rb_rows, chunk_cols,
+        n_buffers, rounds, core_pieces, core_base, rest_start, (float*)core_val, core_rc, (float*)rest_val, rest_row,
+        rest_col);
+  else
+    panel_core_place_kernel<double><<<g, kCoreWarps * 32, 0, st>>>(
+        (const double*)sorted_val, sorted_row, sorted_col, unit_start, unit_rb, unit_ord, n_units, rb_rows, chunk_cols,
+        n_buffers, rounds, core_pieces, core_base, rest_start, (double*)core_val, core_rc, (double*)rest_val, rest_row,
+        rest_col);
   FSB_RETURN_IF_LAUNCH_FAILED();
   return FSB_OK;
 }

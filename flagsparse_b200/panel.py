@@ -376,7 +376,7 @@ def _build_slab(data, indices, indptr, r0, r1, RB, CW, n_ch, rounds, NB, max_slo
     return val, rc, upiece, u_ch, u_rb, n_pieces, max_run, n_runs
 
 
-FUSED_MAX_TABLE = 1 << 24    # (row blocks x column chunks) cells the device-side builder keeps a dense table of
+FUSED_MAX_TABLE = 1 << 26    # (row blocks x column chunks) cells the device-side builder keeps a dense table of
 _ITYPE = {torch.int32: _lib.FSB_I32, torch.int64: _lib.FSB_I64}
 
 
@@ -390,12 +390,99 @@ def _fused_applicable(data, indices, indptr, n_rows, n_cols, RB, CW):
     return n_ch <= int(_lib.lib().fsb_panel_build_max_chunks()) and n_rb * n_ch <= FUSED_MAX_TABLE
 
 
+def _fused_pieces(L, vt, st, s_val, s_row, s_col, ustart, u_rb, u_ord, n_units, nnz, RB, CW, NB, rounds, max_pieces):
+    """Cut and fill of units given as ranges of sorted entries.  Returns (val, rc, pieces per unit as int64) or None
+    when there would be more than max_pieces pieces."""
+    dev = s_row.device
+    SLOTS = 32 * rounds
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    pcount = torch.empty(n_units, dtype=torch.int32, device=dev)
+    _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, None, pcount.data_ptr(), None,
+                                     flag.data_ptr(), st), "fsb_panel_build_cut")
+    upiece = _cumsum0(pcount.to(torch.int64))
+    n_pieces = int(upiece[-1].item())                                 # a sync
+    if n_pieces >= 2**31 - 1 or (max_pieces is not None and n_pieces > max_pieces):
+        return None
+    upiece = upiece.to(torch.int32)
+    pstart = torch.empty(n_pieces + 1, dtype=torch.int32, device=dev)
+    pstart[-1] = nnz
+    _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, upiece.data_ptr(), None,
+                                     pstart.data_ptr(), flag.data_ptr(), st), "fsb_panel_build_cut")
+    val = torch.empty(n_pieces * SLOTS, dtype=s_val.dtype, device=dev)
+    rc = torch.empty(n_pieces * SLOTS, dtype=torch.int32, device=dev)
+    _lib.check(L.fsb_panel_build_fill(vt, s_val.data_ptr(), s_row.data_ptr(), s_col.data_ptr(), pstart.data_ptr(),
+                                      upiece.data_ptr(), n_units, u_rb.data_ptr(), u_ord.data_ptr(), n_pieces, RB, CW, NB,
+                                      rounds, val.data_ptr(), rc.data_ptr(), st), "fsb_panel_build_fill")
+    return val, rc, pcount.to(torch.int64)
+
+
+def _fused_core(L, vt, st, s_val, s_row, s_col, ustart, u_rb, u_ord, n_units, nnz, RB, CW, NB, rounds, max_slots):
+    """The device-side form of pack_pieces_core.  Returns (val, rc, pieces per unit), None (too much padding), or
+    "plain" when the core pieces would hold less than a quarter of the entries."""
+    dev = s_row.device
+    SLOTS = 32 * rounds
+    J = torch.empty(n_units, dtype=torch.int32, device=dev)
+    n_rest = torch.empty(n_units, dtype=torch.int32, device=dev)
+    _lib.check(L.fsb_panel_build_core_count(s_row.data_ptr(), ustart.data_ptr(), u_rb.data_ptr(), n_units, RB, rounds,
+                                            J.data_ptr(), n_rest.data_ptr(), st), "fsb_panel_build_core_count")
+    J64 = J.to(torch.int64)
+    core_total = int(J64.sum().item())                                # a sync
+    if core_total * SLOTS * 4 < nnz:
+        return "plain"
+    rest_total = nnz - core_total * SLOTS
+    core_base = _cumsum0(J64).to(torch.int32)
+    rest_start = _cumsum0(n_rest.to(torch.int64)).to(torch.int32)
+    core_val = torch.empty(core_total * SLOTS, dtype=s_val.dtype, device=dev)
+    core_rc = torch.empty(core_total * SLOTS, dtype=torch.int32, device=dev)
+    r_val = torch.empty(max(rest_total, 1), dtype=s_val.dtype, device=dev)
+    r_row = torch.empty(max(rest_total, 1), dtype=torch.int32, device=dev)
+    r_col = torch.empty(max(rest_total, 1), dtype=torch.int32, device=dev)
+    _lib.check(L.fsb_panel_build_core_place(vt, s_val.data_ptr(), s_row.data_ptr(), s_col.data_ptr(), ustart.data_ptr(),
+                                            u_rb.data_ptr(), u_ord.data_ptr(), n_units, RB, CW, NB, rounds, J.data_ptr(),
+                                            core_base.data_ptr(), rest_start.data_ptr(), core_val.data_ptr(),
+                                            core_rc.data_ptr(), r_val.data_ptr(), r_row.data_ptr(), r_col.data_ptr(), st),
+               "fsb_panel_build_core_place")
+    Lp = torch.zeros(n_units, dtype=torch.int64, device=dev)          # pieces of the rest, per unit
+    rest_pieces = 0
+    if rest_total > 0:
+        has = n_rest > 0
+        has_units = torch.nonzero(has, as_tuple=False).flatten()
+        r_ustart = _cumsum0(n_rest[has].to(torch.int64)).to(torch.int32)
+        packed = _fused_pieces(L, vt, st, r_val, r_row, r_col, r_ustart, u_rb[has].contiguous(), u_ord[has].contiguous(),
+                               has_units.numel(), rest_total, RB, CW, NB, rounds, None)
+        if packed is None:
+            return None
+        p_val, p_rc, p_cnt = packed
+        Lp[has_units] = p_cnt
+        r_upiece = _cumsum0(p_cnt)
+        rest_pieces = int(p_val.numel() // SLOTS)
+    upiece = _cumsum0(J64 + Lp)
+    n_pieces = core_total + rest_pieces
+    if max_slots is not None and n_pieces * SLOTS > max_slots:
+        return None
+    val = torch.empty(n_pieces * SLOTS, dtype=s_val.dtype, device=dev)
+    rc = torch.empty(n_pieces * SLOTS, dtype=torch.int32, device=dev)
+    q = torch.arange(core_total, device=dev)
+    cu = torch.searchsorted(core_base.to(torch.int64), q, right=True) - 1     # unit of every core piece
+    dst = upiece[cu] + (q - core_base.to(torch.int64)[cu])
+    val.view(n_pieces, SLOTS)[dst] = core_val.view(core_total, SLOTS)
+    rc.view(n_pieces, SLOTS)[dst] = core_rc.view(core_total, SLOTS)
+    del core_val, core_rc, q, cu, dst
+    if rest_pieces > 0:
+        q = torch.arange(rest_pieces, device=dev)
+        cu = torch.searchsorted(r_upiece, q, right=True) - 1                  # (compacted) unit of every rest piece
+        ru = has_units[cu]
+        dst = upiece[ru] + J64[ru] + (q - r_upiece[cu])
+        val.view(n_pieces, SLOTS)[dst] = p_val.view(rest_pieces, SLOTS)
+        rc.view(n_pieces, SLOTS)[dst] = p_rc.view(rest_pieces, SLOTS)
+    return val, rc, J64 + Lp
+
+
 def _build_fused(data, indices, indptr, n_rows, n_cols, geometry, NB, rounds, force):
-    """The layout built by the kernels of csrc/panel_build.cu (count, sort, runs, cut, fill) with three host
-    synchronisations, bit-identical to what _build_slab + pack_pieces give.  Returns a PanelLayout; None when the
-    matrix should not (or cannot) take the panel kernel; or the string "host" when the host-side builder has to do
-    it: entries of a tile spread over too many chunks for the sort pass, or a float32 matrix with mostly one entry
-    per row and unit, whose core pieces (pack_pieces_core) only the host-side builder makes."""
+    """The layout built by the kernels of csrc/panel_build.cu (count, sort, runs, core pieces, cut, fill) with a few
+    host synchronisations, bit-identical to what _build_slab + pack_pieces_core give.  Returns a PanelLayout; None when
+    the matrix should not (or cannot) take the panel kernel; or the string "host" when the host-side builder has to do
+    it (1024 consecutive entries spread over more chunks than the sort pass has room for)."""
     L = _lib.lib()
     vt, sv, CW, RB = geometry
     dev = data.device
@@ -416,55 +503,59 @@ def _build_fused(data, indices, indptr, n_rows, n_cols, geometry, NB, rounds, fo
         ustart = _cumsum0(cnt[cell].to(torch.int64)).to(torch.int32)
         unit_base = torch.zeros(n_rb * n_ch, dtype=torch.int32, device=dev)
         unit_base[cell] = ustart[:-1]
-        u_rb = (cell // n_ch).to(torch.int32)
+        del cnt
+        rb_of_unit = cell // n_ch
+        u_rb = rb_of_unit.to(torch.int32)
         u_ch = (cell % n_ch).to(torch.int32)
-        rb_unit_ptr = _cumsum0(torch.bincount(cell // n_ch, minlength=n_rb)).to(torch.int32)
+        rb_unit_ptr64 = _cumsum0(torch.bincount(rb_of_unit, minlength=n_rb))
+        rb_unit_ptr = rb_unit_ptr64.to(torch.int32)
+        u_ord = (torch.arange(n_units, device=dev) - rb_unit_ptr64[rb_of_unit]).to(torch.int32)
+        del cell, rb_of_unit, rb_unit_ptr64
         s_val = torch.empty(nnz, dtype=data.dtype, device=dev)
         s_row = torch.empty(nnz, dtype=torch.int32, device=dev)
         s_col = torch.empty(nnz, dtype=torch.int32, device=dev)
-        flag = torch.zeros(2, dtype=torch.int32, device=dev)
         stats = torch.empty(5, dtype=torch.int64, device=dev)
-        _lib.check(L.fsb_panel_build_sort(vt, it, pt, data.data_ptr(), indices.data_ptr(), indptr.data_ptr(), n_rows,
-                                          n_cols, RB, CW, unit_base.data_ptr(), s_val.data_ptr(), s_row.data_ptr(),
-                                          s_col.data_ptr(), flag.data_ptr(), st), "fsb_panel_build_sort")
-        _lib.check(L.fsb_panel_build_runs(s_row.data_ptr(), s_col.data_ptr(), nnz, CW, stats.data_ptr(), st),
-                   "fsb_panel_build_runs")
-        del unit_base, cnt
-        failed = int(flag[0].item())                                  # a sync
+        # the narrow window where a row block has few units (a tile's chunks are among them), else the wide one
+        wide = n_units > (int(L.fsb_panel_build_window(0)) * 3 // 4) * n_rb
+        while True:
+            flag = torch.zeros(1, dtype=torch.int32, device=dev)
+            _lib.check(L.fsb_panel_build_sort(vt, it, pt, data.data_ptr(), indices.data_ptr(), indptr.data_ptr(), n_rows,
+                                              n_cols, RB, CW, int(wide), unit_base.data_ptr(), s_val.data_ptr(),
+                                              s_row.data_ptr(), s_col.data_ptr(), flag.data_ptr(), st),
+                       "fsb_panel_build_sort")
+            _lib.check(L.fsb_panel_build_runs(s_row.data_ptr(), s_col.data_ptr(), nnz, CW, stats.data_ptr(), st),
+                       "fsb_panel_build_runs")
+            if not int(flag.item()):                                   # a sync
+                break
+            if wide:
+                return "host"
+            wide = True
+        del unit_base
         n_runs, max_run, *long_runs = (int(v) for v in stats.tolist())
-        if failed:
-            return "host"
-        if sv == 4 and nnz < RUNS_MIN_MEAN * n_runs and not os.environ.get("FSB_PANEL_NO_CORE"):
-            return "host"
         rounds = rounds or choose_rounds(long_runs)
+        core = sv == 4 and nnz < RUNS_MIN_MEAN * n_runs and not os.environ.get("FSB_PANEL_NO_CORE")
         while True:
             SLOTS = 32 * rounds
             packed = None
             if max_run <= SLOTS:
-                pcount = torch.empty(n_units, dtype=torch.int32, device=dev)
-                _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, None,
-                                                 pcount.data_ptr(), None, flag[1:].data_ptr(), st),
-                           "fsb_panel_build_cut")
-                upiece = _cumsum0(pcount.to(torch.int64))
-                n_pieces = int(upiece[-1].item())                     # a sync
-                if n_pieces < 2**31 - 1 and (force or n_pieces * SLOTS <= MAX_SLOT_OVERHEAD * nnz + 4096):
-                    packed = upiece.to(torch.int32)
+                max_slots = None if force else int(MAX_SLOT_OVERHEAD * nnz + 4096)
+                if core:
+                    packed = _fused_core(L, vt, st, s_val, s_row, s_col, ustart, u_rb, u_ord, n_units, nnz, RB, CW, NB,
+                                         rounds, max_slots)
+                    if isinstance(packed, str):
+                        core, packed = False, None
+                        continue
+                else:
+                    packed = _fused_pieces(L, vt, st, s_val, s_row, s_col, ustart, u_rb, u_ord, n_units, nnz, RB, CW, NB,
+                                           rounds, None if max_slots is None else max_slots // SLOTS)
             if packed is not None:
                 break
             if rounds == ROUNDS[-1]:
                 return None
             rounds = ROUNDS[-1]      # a run that does not fit a small piece, or too much padding
-        upiece = packed
-        pstart = torch.empty(n_pieces + 1, dtype=torch.int32, device=dev)
-        pstart[-1] = nnz
-        _lib.check(L.fsb_panel_build_cut(s_row.data_ptr(), ustart.data_ptr(), n_units, SLOTS, upiece.data_ptr(), None,
-                                         pstart.data_ptr(), flag[1:].data_ptr(), st), "fsb_panel_build_cut")
-        val = torch.empty(n_pieces * SLOTS, dtype=data.dtype, device=dev)
-        rc = torch.empty(n_pieces * SLOTS, dtype=torch.int32, device=dev)
-        _lib.check(L.fsb_panel_build_fill(vt, s_val.data_ptr(), s_row.data_ptr(), s_col.data_ptr(), pstart.data_ptr(),
-                                          upiece.data_ptr(), n_units, u_rb.data_ptr(), rb_unit_ptr.data_ptr(), n_pieces,
-                                          RB, CW, NB, rounds, val.data_ptr(), rc.data_ptr(), st),
-                   "fsb_panel_build_fill")
+        val, rc, per_unit = packed
+        upiece = _cumsum0(per_unit).to(torch.int32)
+        n_pieces = val.numel() // SLOTS
     lay = PanelLayout()
     lay.val, lay.rc = val, rc
     lay.unit_piece_ptr, lay.unit_chunk, lay.rb_unit_ptr = upiece, u_ch, rb_unit_ptr

@@ -229,7 +229,8 @@ int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, co
  *   sort   the entries in unit order (units = non-empty (rb, c) cells in row-major cell order; inside a unit the CSR
  *          order is kept): sorted_val / sorted_row (global row) / sorted_col (global column), nnz < 2^31 elements each;
  *          unit_base[rb * n_ch + c] = position of the unit's first entry.  *status (device int32) is set to 1 when 1024
- *          consecutive entries of the matrix span more than 128 chunks -- the caller then falls back to another builder
+ *          consecutive entries of the matrix span more than fsb_panel_build_window(wide_window) chunks -- the caller
+ *          then falls back to another builder (the wide window costs more per tile: for wide bands only)
  *   runs   stats[0..4] (device int64) = runs (consecutive sorted entries of one row in one unit), longest run, runs
  *          longer than 4 / 8 / 16 entries
  *   cut    greedy cuts of every unit into pieces of at most `slots` entries that split no run.  With piece_start ==
@@ -238,14 +239,22 @@ int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, co
  *          longer than a piece
  *   fill   val / rc of fsb_spmv_csr_panel (n_pieces * 32 * rounds slots): per piece, entries in stable order of
  *          (local row mod 32 for float32, mod 16 for float64), slot s of that order in lane s / rounds, round s % rounds;
- *          unit_rb[u] = row block of unit u; unused slots carry value 0 and the spare accumulator rb_rows
+ *          unit_rb[u] = row block of unit u, unit_ord[u] = its ordinal inside that row block (picks the x buffer);
+ *          unused slots carry value 0 and the spare accumulator rb_rows
+ *   core_count / core_place (float32 layouts whose rows mostly have one entry per unit): the entries alone in their run,
+ *          listed per class (local row mod 32) in unit order, fill core_pieces[u] = (shortest list) / rounds pieces of
+ *          unit u completely, lane = class, so that a round's 32 accumulators lie in 32 banks; core_place writes those
+ *          pieces (core_base[u] = first of them in core_val / core_rc) and copies every other entry, in order, to
+ *          rest_val / rest_row / rest_col from rest_start[u] on, for cut and fill to treat like an ordinary unit
  */
 int fsb_panel_build_max_chunks(void);
 int fsb_panel_build_count(int itype, int ptype, const void* indices, const void* indptr, int64_t n_rows,
                           int64_t n_cols, int32_t rb_rows, int32_t chunk_cols, int32_t* cnt, void* stream);
 int fsb_panel_build_sort(int vtype, int itype, int ptype, const void* data, const void* indices, const void* indptr,
-                         int64_t n_rows, int64_t n_cols, int32_t rb_rows, int32_t chunk_cols, const int32_t* unit_base,
-                         void* sorted_val, int32_t* sorted_row, int32_t* sorted_col, int32_t* status, void* stream);
+                         int64_t n_rows, int64_t n_cols, int32_t rb_rows, int32_t chunk_cols, int32_t wide_window,
+                         const int32_t* unit_base, void* sorted_val, int32_t* sorted_row, int32_t* sorted_col,
+                         int32_t* status, void* stream);
+int fsb_panel_build_window(int wide);
 int fsb_panel_build_runs(const int32_t* sorted_row, const int32_t* sorted_col, int64_t nnz, int32_t chunk_cols,
                          int64_t* stats, void* stream);
 int fsb_panel_build_cut(const int32_t* sorted_row, const int32_t* unit_start, int32_t n_units, int32_t slots,
@@ -253,8 +262,17 @@ int fsb_panel_build_cut(const int32_t* sorted_row, const int32_t* unit_start, in
                         void* stream);
 int fsb_panel_build_fill(int vtype, const void* sorted_val, const int32_t* sorted_row, const int32_t* sorted_col,
                          const int32_t* piece_start, const int32_t* unit_piece_ptr, int32_t n_units,
-                         const int32_t* unit_rb, const int32_t* rb_unit_ptr, int32_t n_pieces, int32_t rb_rows,
+                         const int32_t* unit_rb, const int32_t* unit_ord, int32_t n_pieces, int32_t rb_rows,
                          int32_t chunk_cols, int32_t n_buffers, int32_t rounds, void* val, uint32_t* rc, void* stream);
+int fsb_panel_build_core_count(const int32_t* sorted_row, const int32_t* unit_start, const int32_t* unit_rb,
+                               int32_t n_units, int32_t rb_rows, int32_t rounds, int32_t* core_pieces,
+                               int32_t* rest_count, void* stream);
+int fsb_panel_build_core_place(int vtype, const void* sorted_val, const int32_t* sorted_row, const int32_t* sorted_col,
+                               const int32_t* unit_start, const int32_t* unit_rb, const int32_t* unit_ord,
+                               int32_t n_units, int32_t rb_rows, int32_t chunk_cols, int32_t n_buffers, int32_t rounds,
+                               const int32_t* core_pieces, const int32_t* core_base, const int32_t* rest_start,
+                               void* core_val, uint32_t* core_rc, void* rest_val, int32_t* rest_row, int32_t* rest_col,
+                               void* stream);
 
 #define FSB_NOALLOC_MAX_TILES 262144
 int fsb_spmv_csr_noalloc(int vtype, int itype, int ptype, const void* data, const void* indices,

@@ -71,12 +71,17 @@ def test_banded_matrices(cuda, fsb_lib, vdt, name, rows):
     prep.check_status()
 
 
-def test_single_entry_float32_layouts_go_to_the_host_builder(cuda, fsb_lib):
-    spec = S.config_spec("c5").scaled(400000)
-    d, i, p = S.generate_csr(spec, "cuda:0")
-    assert _is_fused(d, i, p, spec.n_rows, spec.n_cols) == "host"          # core pieces
-    a, b = _both(d, i, p, spec.n_rows, spec.n_cols)
-    _assert_same(a, b, "c5 float32 with core pieces")
+@pytest.mark.parametrize("rows", [400000, 1 << 22])
+def test_core_pieces(cuda, fsb_lib, rows):
+    """float32 layouts with mostly one entry per row and unit: core pieces + rest, as pack_pieces_core makes them.
+    The larger case has some 200 chunks per row block: the sort pass takes its wide window."""
+    spec = S.config_spec("c5").scaled(rows)
+    d, i, p = S.generate_csr(spec, "cuda:0", indptr_dtype="int64")
+    assert _is_fused(d, i, p, spec.n_rows, spec.n_cols) == "fused"
+    for rounds in ((None, 4, 16) if rows < (1 << 22) else (None,)):
+        a, b = _both(d, i, p, spec.n_rows, spec.n_cols, rounds=rounds)
+        assert a is not None and not a.flags & P.FLAG_RUNS
+        _assert_same(a, b, f"c5 float32 with core pieces, {rows} rows, rounds {rounds}")
 
 
 def test_long_runs_every_piece_size(cuda, fsb_lib):
@@ -125,10 +130,10 @@ def test_ragged_unsorted_duplicates(cuda, fsb_lib, vdt, idt, pdt):
 
 def test_columns_spread_too_widely_fall_back_to_the_host_builder(cuda, fsb_lib):
     lens = [40] * 60000
-    data, idx, ptr = handmade_csr(5, lens, 3_000_000, replace=True)   # uniform columns: hundreds of chunks per tile
+    data, idx, ptr = handmade_csr(5, lens, 12_000_000, replace=True)   # uniform columns: hundreds of chunks per tile
     d, i, p = dev(data), dev(idx), dev(ptr)
-    assert _is_fused(d, i, p, len(lens), 3_000_000) == "host"
-    a, b = _both(d, i, p, len(lens), 3_000_000)
+    assert _is_fused(d, i, p, len(lens), 12_000_000) == "host"
+    a, b = _both(d, i, p, len(lens), 12_000_000)
     _assert_same(a, b, "wide columns")
 
 
