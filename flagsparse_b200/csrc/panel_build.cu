@@ -1,17 +1,20 @@
 // Device-side construction of the panel layout (the regrouping that fsb_spmv_csr_panel multiplies from).
 //
-// Five passes over the matrix, each one kernel, so that preparing a matrix costs a handful of products instead of
-// hundreds:
+// A few passes over the matrix, each one kernel, so that preparing a matrix costs tens of products instead of
+// hundreds or thousands:
 //   count   entries per (row block, column chunk), one CTA per row block, counted in shared memory
 //   sort    every entry to its place in unit order -- units by (row block, chunk), inside a unit the entries keep
 //           their CSR order (a stable counting sort: one CTA per row block walks its entries in tiles of 1024)
 //   runs    statistics of the runs (consecutive entries of one row inside one unit): how many, the longest, how
 //           many longer than 4 / 8 / 16 -- they decide the piece size and the kernel mode
-//   cut     greedy cuts of every unit into pieces of at most `slots` entries that never split a run
+//   core    (layouts with mostly one entry per row and unit) the single entries of every accumulator class fill
+//           "core" pieces in which lane l only meets accumulators congruent to l modulo 32; the rest is copied out
+//   cut     greedy cuts of every unit (or of its rest) into pieces of at most `slots` entries that never split a run
 //   fill    one warp per piece: entries ordered by the shared-memory bank of their accumulator (stable), then
 //           written to the interleaved slot positions the kernel loads from; unused slots get the spare accumulator
-// The small tables in between (unit list, prefix sums) are made by the host code from the count pass's table.
-// The result is bit-identical to the host-side reference builder (flagsparse_b200/panel.py: pack_pieces).
+// The small tables in between (unit list, prefix sums, the final order of core and rest pieces) are made by the host
+// code.  The result is bit-identical to the host-side reference builder (flagsparse_b200/panel.py: _build_slab,
+// pack_pieces, pack_pieces_core).
 #include <limits.h>
 
 #include "fsb_common.cuh"

@@ -223,7 +223,7 @@ int fsb_spmv_csr_panel_groups(int vtype, const void* val, const uint32_t* rc, co
  */
 /*
  * Construction of the panel layout on the device (the reference has no counterpart: its prepare step builds row
- * buckets, spmv_csr.py:281-327).  Five passes, called in this order by flagsparse_b200/panel.py, every array caller-owned:
+ * buckets, spmv_csr.py:281-327).  Passes called in this order by flagsparse_b200/panel.py, every array caller-owned:
  *   count  cnt[rb * n_ch + c] = entries of row block rb (rb_rows rows) in column chunk c (chunk_cols columns);
  *          n_ch = ceil(n_cols / chunk_cols) <= fsb_panel_build_max_chunks()
  *   sort   the entries in unit order (units = non-empty (rb, c) cells in row-major cell order; inside a unit the CSR
