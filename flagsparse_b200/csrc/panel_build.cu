@@ -96,10 +96,18 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
   }
   __syncthreads();
   const int64_t e0 = (int64_t)ptr[r0], e1 = (int64_t)ptr[r1];
+  // the next tile's column and value are requested while this tile is placed
+  I col_next = (e0 + tid) < e1 ? idx[e0 + tid] : (I)0;
+  V val_next = (e0 + tid) < e1 ? data[e0 + tid] : (V)0;
   for (int64_t base = e0; base < e1; base += kBuildThreads) {
     const int64_t e = base + tid;
     const bool live = e < e1;
-    const I col = live ? idx[e] : (I)0;
+    const I col = col_next;
+    const V val_here = val_next;
+    if (e + kBuildThreads < e1) {
+      col_next = idx[e + kBuildThreads];
+      val_next = data[e + kBuildThreads];
+    }
     const int c = live ? chunk_of(col, chunk_cols) : INT_MAX;
     const int wm = warp_min_i(c);
     if (lane == 0) s_min[warp] = wm;
@@ -155,7 +163,7 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
         if ((int64_t)ptr[mid] <= e) lo = mid;
         else hi = mid - 1;
       }
-      o_val[pos] = data[e];
+      o_val[pos] = val_here;
       o_row[pos] = (int32_t)lo;
       o_col[pos] = (int32_t)col;
       if (tid == kBuildThreads - 1) s_tile_row = lo;   // the next tile's entries are in this row or behind it
