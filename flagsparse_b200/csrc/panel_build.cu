@@ -82,14 +82,15 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
   // a column (one chunk, all warps) falls into 32 different banks
   __shared__ uint16_t s_cntw[kBuildWarps][kBuildWindow + 2];
   __shared__ int32_t s_tile_base[kBuildWindow];
-  __shared__ int s_min[kBuildWarps];
-  __shared__ int s_tmin, s_fail;
+  __shared__ int s_min[kBuildWarps], s_max[kBuildWarps];
+  __shared__ int s_tmin, s_tmax, s_fail;
   __shared__ long long s_tile_row;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t r0 = (int64_t)blockIdx.x * rb_rows;
   const int64_t r1 = (r0 + rb_rows) < n_rows ? (r0 + rb_rows) : n_rows;
   const int32_t* base_row = unit_base + (int64_t)blockIdx.x * n_ch;
   for (int i = tid; i < n_ch; i += kBuildThreads) s_run[i] = base_row[i];
+  for (int i = tid; i < kBuildWarps * (kBuildWindow + 2); i += kBuildThreads) (&s_cntw[0][0])[i] = 0;
   if (tid == 0) {
     s_fail = 0;
     s_tile_row = r0;
@@ -110,15 +111,24 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
     }
     const int c = live ? chunk_of(col, chunk_cols) : INT_MAX;
     const int wm = warp_min_i(c);
-    if (lane == 0) s_min[warp] = wm;
-    for (int i = tid; i < kBuildWarps * (kBuildWindow + 2); i += kBuildThreads) (&s_cntw[0][0])[i] = 0;
+    const int wx = -warp_min_i(live ? -c : 0);           // chunks are >= 0: a dead lane does not raise the maximum
+    if (lane == 0) {
+      s_min[warp] = wm;
+      s_max[warp] = wx;
+    }
     __syncthreads();
     if (warp == 0) {
       const int m = warp_min_i(s_min[lane]);
-      if (lane == 0) s_tmin = m;
+      const int x = -warp_min_i(-s_max[lane]);
+      if (lane == 0) {
+        s_tmin = m;
+        s_tmax = x;
+      }
     }
     __syncthreads();
     const int tmin = s_tmin;
+    // chunks of the window this tile uses; only they are scanned below and cleared for the next tile
+    const int span = (s_tmax - tmin + 1) < kBuildWindow ? (s_tmax - tmin + 1) : kBuildWindow;
     const int64_t tile_row = s_tile_row;
     const int b = live ? (c - tmin) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, b);
@@ -131,7 +141,7 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
     if (s_fail) break;                                   // the same answer for every thread
     // per chunk of the window: exclusive prefix of the 32 warps' counts (lane = source warp), then the unit's
     // running offset moves on by the total; warp w looks after chunks w, w + 32, ...
-    for (int bin = warp; bin < kBuildWindow; bin += kBuildWarps) {
+    for (int bin = warp; bin < span; bin += kBuildWarps) {
       const int mine = s_cntw[lane][bin];
       int incl = mine;
 #pragma unroll
@@ -168,7 +178,8 @@ panel_sort_kernel(const V* __restrict__ data, const I* __restrict__ idx, const P
       o_col[pos] = (int32_t)col;
       if (tid == kBuildThreads - 1) s_tile_row = lo;   // the next tile's entries are in this row or behind it
     }
-    __syncthreads();   // the tables are rewritten by the next tile
+    __syncthreads();   // every read of the tables is done
+    for (int bin = lane; bin < span; bin += 32) s_cntw[warp][bin] = 0;   // two barriers ahead of the next writes
   }
   if (s_fail && tid == 0) *status = 1;
 }
