@@ -47,9 +47,9 @@ FALLBACK_HBM_GBS = 6650.0
 # and of the entries), scaled by 16.
 _PANEL_SOURCES = ("flagsparse_b200/csrc/spmv_panel.cu", "flagsparse_b200/panel.py")
 NCU_TRAFFIC_BYTES = {
-    "c2": (1_097_973_000 + 4_892_672, _PANEL_SOURCES, "d77291e291ef"),        # profiles/spmv_panel_c2_f32.md
-    "c2f64": (1_673_750_000 + 4_101_376, _PANEL_SOURCES, "d77291e291ef"),     # profiles/spmv_panel_c2_f64.md
-    "c5": (16 * (1_127_045_000 + 3_713_792), _PANEL_SOURCES, "d77291e291ef"),  # profiles/spmv_panel_c5like_f32.md
+    "c2": (1_097_973_000 + 4_892_672, _PANEL_SOURCES, "2536da0b2366"),        # profiles/spmv_panel_c2_f32.md
+    "c2f64": (1_673_750_000 + 4_101_376, _PANEL_SOURCES, "2536da0b2366"),     # profiles/spmv_panel_c2_f64.md
+    "c5": (16 * (1_127_045_000 + 3_713_792), _PANEL_SOURCES, "2536da0b2366"),  # profiles/spmv_panel_c5like_f32.md
 }
 
 SPMV_WORKLOADS = {

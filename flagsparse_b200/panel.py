@@ -3,8 +3,10 @@
 The reference's prepare step builds row-length buckets (src/flagsparse/sparse_operations/spmv_csr.py:281-327);
 this one builds, for matrices whose rows reach a limited range of columns, a second copy of the entries
 grouped into units = (block of RB rows) x (chunk of CW columns), so that the kernel can keep the part of x a
-unit needs in shared memory.  It runs once per matrix, off the timed path, with torch operations on the
-device; the product itself is one launch of fsb_spmv_csr_panel.
+unit needs in shared memory.  It runs once per matrix, off the timed path: by the kernels of
+csrc/panel_build.cu (_build_fused) where they apply, else by torch operations on the device (_build_slab,
+pack_pieces, pack_pieces_core -- also the reference the kernels are tested against, bit for bit); the product
+itself is one launch of fsb_spmv_csr_panel.
 """
 
 import os
