@@ -62,6 +62,34 @@ def test_checking_build_exports_the_same_symbols(fsb_lib):
         _lib.check(-1, "x")
 
 
+def test_layout_builder_refuses_bad_arguments_on_the_host(fsb_lib):
+    """The entry points of the device-side layout builder check enums, sizes and pointers before any launch."""
+    L, F32, I32 = fsb_lib, _lib.FSB_F32, _lib.FSB_I32
+    assert L.fsb_panel_build_max_chunks() == 32768
+    assert L.fsb_panel_build_window(0) == 128 and L.fsb_panel_build_window(1) == 640
+    assert L.fsb_panel_build_count(7, I32, None, None, 4, 4, 1024, 4096, None, None) == -1          # bad index type
+    assert L.fsb_panel_build_count(I32, I32, None, None, 4, 4, 0, 4096, None, None) == -1           # no rows per block
+    assert L.fsb_panel_build_count(I32, I32, None, None, 0, 4, 1024, 4096, None, None) == 0         # nothing to count
+    assert L.fsb_panel_build_count(I32, I32, None, None, 4, 4, 1024, 4096, None, None) == -1        # missing arrays
+    assert L.fsb_panel_build_sort(F32, I32, I32, None, None, None, 4, 4, 1024, 4096, 0, None, None, None, None, None,
+                                  None) == -1
+    assert L.fsb_panel_build_sort(9, I32, I32, None, None, None, 4, 4, 1024, 4096, 0, None, None, None, None, None,
+                                  None) == -1
+    assert L.fsb_panel_build_runs(None, None, -1, 4096, None, None) == -1
+    assert L.fsb_panel_build_cut(None, None, 0, 512, None, None, None, None, None) == -1            # no status word
+    assert L.fsb_panel_build_cut(None, None, -1, 512, None, None, None, None, None) == -1
+    assert L.fsb_panel_build_fill(F32, None, None, None, None, None, 1, None, None, 1, 1024, 4096, 2, 5, None, None,
+                                  None) == -1                                                        # 5 rounds
+    assert L.fsb_panel_build_fill(F32, None, None, None, None, None, 1, None, None, 0, 1024, 4096, 2, 8, None, None,
+                                  None) == 0                                                         # no pieces
+    assert L.fsb_panel_build_fill(F32, None, None, None, None, None, 1, None, None, 1, 1024, 40000, 2, 8, None, None,
+                                  None) == -1                                                        # x slots > 65536
+    assert L.fsb_panel_build_core_count(None, None, None, 3, 1024, 8, None, None, None) == -1
+    assert L.fsb_panel_build_core_count(None, None, None, 0, 1024, 8, None, None, None) == 0
+    assert L.fsb_panel_build_core_place(F32, None, None, None, None, None, None, 2, 1024, 4096, 2, 8, None, None, None,
+                                        None, None, None, None, None, None) == -1
+
+
 def test_argument_errors_are_reported_before_any_launch(fsb_lib):
     # bad enums / sizes are rejected on the host, so this needs no device
     assert fsb_lib.fsb_spmv_csr(7, 0, 0, None, None, None, None, None, 1, 1, 0, 0, 0, None, None, 0, None) == -1
