@@ -193,13 +193,14 @@ __device__ __forceinline__ bool run_starts_at(const int32_t* __restrict__ row, c
 
 constexpr int kRunsScanLimit = 1 << 16;   // a run longer than this is longer than any piece anyway
 
-// stats[0] = runs, [1] = longest run, [2..4] = runs longer than 4 / 8 / 16 entries
+// stats[0] = runs, [1] = longest run, [2..4] = runs longer than 4 / 8 / 16 entries.  Positions are kept relative
+// to the CTA's first entry (32-bit: a CTA covers tiles_per_cta * 1024 entries, the look-back at most kRunsScanLimit).
 __global__ void __launch_bounds__(kBuildThreads)
 panel_runs_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ col, int64_t nnz, int chunk_cols,
                   int tiles_per_cta, unsigned long long* __restrict__ stats) {
-  __shared__ long long s_warp_last[kBuildWarps];
-  __shared__ long long s_before[kBuildWarps];
-  __shared__ long long s_carry;
+  __shared__ int s_warp_last[kBuildWarps];
+  __shared__ int s_before[kBuildWarps];
+  __shared__ int s_carry;
   __shared__ unsigned long long s_acc[5];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t first = (int64_t)blockIdx.x * tiles_per_cta * kBuildThreads;
@@ -208,40 +209,43 @@ panel_runs_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ c
     int64_t p = first;
     int steps = 0;
     while (p > 0 && steps < kRunsScanLimit && !run_starts_at(row, col, p, chunk_cols)) { --p; ++steps; }
-    s_carry = p;
+    s_carry = (int)(p - first);                         // <= 0: the start of the run that holds the first entry
   }
   if (tid < 5) s_acc[tid] = 0;
   __syncthreads();
-  unsigned long long n_start = 0, mx = 0, g4 = 0, g8 = 0, g16 = 0;
+  constexpr int kNone = INT_MIN;
+  unsigned long long n_start = 0, g4 = 0, g8 = 0, g16 = 0;
+  int mx = 0;
   for (int t = 0; t < tiles_per_cta; ++t) {
-    const int64_t e = first + (int64_t)t * kBuildThreads + tid;
+    const int rel = t * kBuildThreads + tid;
+    const int64_t e = first + rel;
     const bool live = e < nnz;
     const bool st = live && run_starts_at(row, col, e, chunk_cols);
-    long long last = st ? (long long)e : -1;
+    int last = st ? rel : kNone;                        // the last start at or in front of this entry, within the warp
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const long long other = __shfl_up_sync(0xffffffffu, last, o);
+      const int other = __shfl_up_sync(0xffffffffu, last, o);
       if (lane >= o && other > last) last = other;
     }
     if (lane == 31) s_warp_last[warp] = last;
     __syncthreads();
-    if (warp == 0) {                                   // s_before[w] = the last start in front of warp w
-      long long v = s_warp_last[lane];
+    if (warp == 0) {                                    // s_before[w] = the last start in front of warp w
+      int v = s_warp_last[lane];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const long long other = __shfl_up_sync(0xffffffffu, v, o);
+        const int other = __shfl_up_sync(0xffffffffu, v, o);
         if (lane >= o && other > v) v = other;
       }
-      const long long carry = s_carry;
-      long long excl = __shfl_up_sync(0xffffffffu, v, 1);
+      const int carry = s_carry;
+      int excl = __shfl_up_sync(0xffffffffu, v, 1);
       if (lane == 0 || excl < carry) excl = carry;
       s_before[lane] = excl;
     }
     __syncthreads();
-    const long long before = s_before[warp];
+    const int before = s_before[warp];
     if (last < before) last = before;
     if (live) {
-      const unsigned long long d = (unsigned long long)(e - last);   // entries of the run in front of e
+      const int d = rel - last;                         // entries of the run in front of this one
       n_start += st ? 1 : 0;
       mx = d + 1 > mx ? d + 1 : mx;
       g4 += d == 4;
@@ -257,12 +261,12 @@ panel_runs_kernel(const int32_t* __restrict__ row, const int32_t* __restrict__ c
     g4 += __shfl_xor_sync(0xffffffffu, g4, o);
     g8 += __shfl_xor_sync(0xffffffffu, g8, o);
     g16 += __shfl_xor_sync(0xffffffffu, g16, o);
-    const unsigned long long om = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int om = __shfl_xor_sync(0xffffffffu, mx, o);
     mx = om > mx ? om : mx;
   }
   if (lane == 0) {
     atomicAdd(&s_acc[0], n_start);
-    atomicMax(&s_acc[1], mx);
+    atomicMax(&s_acc[1], (unsigned long long)mx);
     atomicAdd(&s_acc[2], g4);
     atomicAdd(&s_acc[3], g8);
     atomicAdd(&s_acc[4], g16);
